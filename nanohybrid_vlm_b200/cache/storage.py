@@ -13,52 +13,70 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import CacheView, FixedStateNeed, PagedKVNeed
+from ..parts.base import CacheView, CompositeNeed, FixedStateNeed, PagedKVNeed
 from .manager import GroupSpec
+
+
+def leaves(need) -> list:
+    """The paged / fixed-state needs that a run's need is made of (a composite's entries, flattened in order)."""
+    if need is None:
+        return []
+    if isinstance(need, CompositeNeed):
+        return [leaf for sub in need.parts for leaf in leaves(sub)]
+    return [need]
 
 
 @dataclass
 class CacheLayout:
-    """Which group each run belongs to (None: the run keeps no pages)."""
+    """Which group each run belongs to (None: the run keeps no pages).  A run whose mixer keeps several things
+    (:class:`CompositeNeed`) has one entry per thing in ``leaf_group``; ``run_group`` names its first paged one."""
     groups: list[GroupSpec]
     run_group: list[int | None]
     needs: list
+    leaf_group: list[list[int | None]] | None = None
 
     @classmethod
     def from_needs(cls, needs: list) -> "CacheLayout":
         groups: list[GroupSpec] = []
         run_group: list[int | None] = []
+        leaf_group: list[list[int | None]] = []
         for need in needs:
-            if isinstance(need, PagedKVNeed):
-                g = GroupSpec(need.window)
-                if g not in groups:
-                    groups.append(g)
-                run_group.append(groups.index(g))
-            else:
-                run_group.append(None)
-        return cls(groups, run_group, list(needs))
+            mine: list[int | None] = []
+            for leaf in leaves(need):
+                if isinstance(leaf, PagedKVNeed):
+                    g = GroupSpec(leaf.window)
+                    if g not in groups:
+                        groups.append(g)
+                    mine.append(groups.index(g))
+                else:
+                    mine.append(None)
+            leaf_group.append(mine)
+            run_group.append(next((g for g in mine if g is not None), None))
+        return cls(groups, run_group, list(needs), leaf_group)
 
     @property
     def needs_state_slots(self) -> bool:
-        return any(isinstance(n, FixedStateNeed) for n in self.needs)
+        return any(isinstance(leaf, FixedStateNeed) for n in self.needs for leaf in leaves(n))
 
     def page_bytes(self, page_size: int, dtype: torch.dtype) -> list[int]:
         """Bytes that one page id of each group stands for (summed over the group's runs)."""
         item = torch.empty((), dtype=dtype).element_size()
         out = [0] * len(self.groups)
-        for need, g in zip(self.needs, self.run_group):
-            if g is not None:
-                out[g] += 2 * need.num_kv_heads * page_size * need.head_dim * item
+        for need, groups in zip(self.needs, self.leaf_group):
+            for leaf, g in zip(leaves(need), groups):
+                if g is not None:
+                    out[g] += 2 * leaf.num_kv_heads * page_size * leaf.row_dim * item
         return out
 
     def state_bytes_per_slot(self, dtype: torch.dtype) -> int:
         total = 0
         for need in self.needs:
-            if isinstance(need, FixedStateNeed):
-                n = 1
-                for s in need.shape:
-                    n *= s
-                total += n * (4 if need.dtype == "float32" else torch.empty((), dtype=dtype).element_size())
+            for leaf in leaves(need):
+                if isinstance(leaf, FixedStateNeed):
+                    n = 1
+                    for s in leaf.shape:
+                        n *= s
+                    total += n * (4 if leaf.dtype == "float32" else torch.empty((), dtype=dtype).element_size())
         return total
 
 
@@ -71,27 +89,45 @@ class CacheStorage:
         self.order = list(order)
         self.page_size = page_size
         self.num_pages = list(num_pages)
+        fill = float("nan") if poison else 0.0
+        # per run, per leaf of its need: (pages, state); ``pages`` / ``states`` keep the first of each kind per run
+        self.leaf_tensors: list[list[tuple]] = []
         self.pages: list[torch.Tensor | None] = []
         self.states: list[torch.Tensor | None] = []
-        for need, g in zip(layout.needs, layout.run_group):
-            if isinstance(need, PagedKVNeed):
-                self.pages.append(torch.full((num_pages[g], 2, need.num_kv_heads, page_size, need.head_dim),
-                                             float("nan") if poison else 0.0, dtype=dtype, device=device))
-                self.states.append(None)
-            elif isinstance(need, FixedStateNeed):
-                sdt = torch.float32 if need.dtype == "float32" else dtype
-                self.pages.append(None)
-                self.states.append(torch.full((max(num_state_slots, 1), *need.shape), float("nan") if poison else 0.0,
-                                              dtype=sdt, device=device))
-            else:
-                self.pages.append(None)
-                self.states.append(None)
+        for need, groups in zip(layout.needs, layout.leaf_group):
+            mine = []
+            for leaf, g in zip(leaves(need), groups):
+                if isinstance(leaf, PagedKVNeed):
+                    mine.append((torch.full((num_pages[g], 2, leaf.num_kv_heads, page_size, leaf.row_dim), fill,
+                                            dtype=dtype, device=device), None))
+                else:
+                    sdt = torch.float32 if leaf.dtype == "float32" else dtype
+                    mine.append((None, torch.full((max(num_state_slots, 1), *leaf.shape), fill, dtype=sdt,
+                                                  device=device)))
+            self.leaf_tensors.append(mine)
+            self.pages.append(next((p for p, _ in mine if p is not None), None))
+            self.states.append(next((s for _, s in mine if s is not None), None))
 
     def view(self, run: int, cache_from: int | None, batch) -> CacheView:
         src = run if cache_from is None else cache_from
-        g = self.layout.run_group[src]
-        return CacheView(pages=self.pages[src], tables=batch.groups[g] if g is not None else None,
-                         writes=cache_from is None, state=self.states[src])
+        writes = cache_from is None
+        need = self.layout.needs[src]
+        if not isinstance(need, CompositeNeed):
+            g = self.layout.run_group[src]
+            return CacheView(pages=self.pages[src], tables=batch.groups[g] if g is not None else None,
+                             writes=writes, state=self.states[src])
+        flat = iter(zip(self.leaf_tensors[src], self.layout.leaf_group[src]))
+
+        def build(n) -> CacheView:
+            if isinstance(n, CompositeNeed):
+                return CacheView(writes=writes, children=tuple(build(sub) for sub in n.parts))
+            if n is None:
+                return CacheView(writes=writes)
+            (pages, state), g = next(flat)
+            return CacheView(pages=pages, tables=batch.groups[g] if g is not None else None, writes=writes, state=state)
+
+        return build(need)
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.pages + self.states if t is not None)
+        return sum(t.numel() * t.element_size() for mine in self.leaf_tensors for pair in mine for t in pair
+                   if t is not None)

@@ -1,4 +1,5 @@
-"""One registry from the architecture's name (``architectures[0]`` of config.json) to its model.
+"""One registry from the architecture's name (``architectures[0]`` of config.json, or its ``architecture``
+string) to its model.
 
 The reference keeps ``model_type -> (architectures, module, class)`` and checks both
 (nanovllm/models/registry.py:36-149).  Here the key is the architecture name; the entry
@@ -42,11 +43,11 @@ class ArchitectureRegistry:
         return sorted(self._entries)
 
     def resolve(self, raw_config: dict) -> ArchitectureEntry:
-        archs = raw_config.get("architectures") or ()
+        archs = raw_config.get("architectures") or raw_config.get("architecture") or ()
         if isinstance(archs, str):
             archs = (archs,)
         if not archs:
-            raise ConfigError("config.json: key 'architectures' is missing or empty; "
+            raise ConfigError("config.json: key 'architectures' (or 'architecture') is missing or empty; "
                               f"supported architectures: {self.names()}")
         known = [a for a in archs if a in self._entries]
         if not known:

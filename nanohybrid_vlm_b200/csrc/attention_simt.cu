@@ -17,6 +17,11 @@
 // sub-group of GS query heads that share it).  A "pair" is (token of the tile, head of
 // the sub-group); pairs are dealt to the 4 warps round-robin, lane <-> key inside a
 // chunk for the scores, lane <-> output column for the weighted sum of values.
+//
+// Two generalisations (nhv_attention_simt_ex): value heads of another size than key heads (dv; a page row holds
+// `row` >= max(d, dv) elements and each kind uses its leading ones), and a sink per query head: a number that joins
+// the softmax denominator as exp(sink) with no key, no value and no scale, counted once.  It enters as the start
+// of the running maximum and sum (m = sink, l = 1), which later chunks rescale like any other term.
 #include <math.h>
 
 #include "nhv_common.cuh"
@@ -33,7 +38,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
                                        const T* __restrict__ kv_pages, const int* __restrict__ block_table,
                                        int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                        int n_seqs, int nq, int nkv, int d, int page_size, int n_pages, int window,
-                                       float scale, int TQ, int GS) {
+                                       float scale, int TQ, int GS, int dv, int row, const float* __restrict__ sinks) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int G = nq / nkv;
@@ -60,8 +65,8 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
 
   const int ks = d + 1;                        // padded key row: lane <-> key reads hit 32 banks
   float* Ks = smem;                            // [32][d+1]
-  float* Vs = Ks + AT_CHUNK * ks;              // [32][d]
-  float* Qs = Vs + AT_CHUNK * d;               // [pairs][d]
+  float* Vs = Ks + AT_CHUNK * ks;              // [32][dv]
+  float* Qs = Vs + AT_CHUNK * dv;              // [pairs][d]
   float* Ps = Qs + AT_MAX_PAIRS * d;           // [warps][32]
   __shared__ int key_ok[AT_CHUNK];
 
@@ -79,6 +84,11 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
   for (int i = 0; i < AT_PAIRS_PER_WARP; ++i) {
     m[i] = -INFINITY;
     l[i] = 0.f;
+    const int p = warp + i * AT_WARPS;
+    if (sinks && p < n_pairs) {
+      m[i] = sinks[kvh * G + g0 + (p % gs)];
+      l[i] = 1.f;
+    }
 #pragma unroll
     for (int c = 0; c < AT_COLS; ++c) o[i][c] = 0.f;
   }
@@ -100,19 +110,20 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
       key_ok[threadIdx.x] = ok;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < AT_CHUNK * d; i += blockDim.x) {
-      const int r = i / d, c = i - r * d;
+    const int dmax = d > dv ? d : dv;
+    for (int i = threadIdx.x; i < AT_CHUNK * dmax; i += blockDim.x) {
+      const int r = i / dmax, c = i - r * dmax;
       float kx = 0.f, vx = 0.f;
       if (key_ok[r]) {
         const int j = c0 + r;
         const int page = block_table[(size_t)seq * bt_stride + j / page_size];
         const int off = j % page_size;
-        const size_t base = ((((size_t)page * 2) * nkv + kvh) * page_size + off) * d + c;
-        kx = to_f32<T>(kv_pages[base]);
-        vx = to_f32<T>(kv_pages[base + (size_t)nkv * page_size * d]);
+        const size_t base = ((((size_t)page * 2) * nkv + kvh) * page_size + off) * row + c;
+        if (c < d) kx = to_f32<T>(kv_pages[base]);
+        if (c < dv) vx = to_f32<T>(kv_pages[base + (size_t)nkv * page_size * row]);
       }
-      Ks[r * ks + c] = kx;
-      Vs[r * d + c] = vx;
+      if (c < d) Ks[r * ks + c] = kx;
+      if (c < dv) Vs[r * dv + c] = vx;
     }
     __syncthreads();
 
@@ -145,9 +156,9 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
 #pragma unroll
       for (int cc = 0; cc < AT_COLS; ++cc) {
         const int c = lane + cc * 32;
-        if (c < d) {
+        if (c < dv) {
           float acc = 0.f;
-          for (int r = 0; r < AT_CHUNK; ++r) acc = fmaf(Ps[warp * AT_CHUNK + r], Vs[r * d + c], acc);
+          for (int r = 0; r < AT_CHUNK; ++r) acc = fmaf(Ps[warp * AT_CHUNK + r], Vs[r * dv + c], acc);
           o[i][cc] = o[i][cc] * alpha + acc;
         }
       }
@@ -161,31 +172,34 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
     if (p >= n_pairs) break;
     const int tq = p / gs, g = p - tq * gs;
     const size_t tok = (size_t)cu_q[seq] + t0 + tq;
-    T* dst = out + tok * out_stride + (size_t)(kvh * G + g0 + g) * d;
+    T* dst = out + tok * out_stride + (size_t)(kvh * G + g0 + g) * dv;
     const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
 #pragma unroll
     for (int cc = 0; cc < AT_COLS; ++cc) {
       const int c = lane + cc * 32;
-      if (c < d) dst[c] = from_f32<T>(o[i][cc] * inv);
+      if (c < dv) dst[c] = from_f32<T>(o[i][cc] * inv);
     }
   }
 }
 
 // max_tiles: an upper bound on sum over requests of ceil(new tokens / TQ); the caller may pass
 // n_tokens / TQ + n_seqs.  Blocks beyond the true count leave at once.
-NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out, int out_stride,
-                               const void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
-                               const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int page_size,
-                               int n_pages, int window, float scale, cudaStream_t stream) {
+NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                                  const void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
+                                  const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int dv, int row,
+                                  int page_size, int n_pages, int window, float scale, const float* sinks,
+                                  cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
-  NHV_REQUIRE(d > 0 && d <= AT_MAX_D, "attention: head size %d is beyond the supported %d", d, AT_MAX_D);
+  NHV_REQUIRE(d > 0 && d <= AT_MAX_D && dv > 0 && dv <= AT_MAX_D, "attention: head sizes %d / %d are beyond the supported %d",
+              d, dv, AT_MAX_D);
+  NHV_REQUIRE(row >= d && row >= dv, "attention: a page row of %d elements does not hold a head of %d / %d", row, d, dv);
   NHV_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
   const int G = nq / nkv;
   const int GS = G < 8 ? G : 8;
   const int TQ = AT_MAX_PAIRS / GS;
   const int max_tiles = n_tokens / TQ + n_seqs;
-  const size_t smem = ((size_t)AT_CHUNK * (d + 1) + (size_t)AT_CHUNK * d + (size_t)AT_MAX_PAIRS * d +
+  const size_t smem = ((size_t)AT_CHUNK * (d + 1) + (size_t)AT_CHUNK * dv + (size_t)AT_MAX_PAIRS * d +
                        AT_WARPS * AT_CHUNK) * sizeof(float);
   dim3 grid(max_tiles, nkv, (G + GS - 1) / GS);
 #define LAUNCH(T)                                                                                              \
@@ -195,7 +209,7 @@ NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out
                                     (int)smem), "attention");                                                  \
     nhv_launch(attn_paged_simt_kernel<T>, grid, AT_WARPS * 32, smem, stream,                                   \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,  \
-        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS);                                        \
+        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks);                        \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
@@ -203,4 +217,12 @@ NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out
 #undef LAUNCH
   NHV_CHECK_LAUNCH("attention");
   return 0;
+}
+
+NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                               const void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
+                               const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int page_size,
+                               int n_pages, int window, float scale, cudaStream_t stream) {
+  return nhv_attention_simt_ex(dtype, q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len,
+                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, scale, nullptr, stream);
 }

@@ -296,6 +296,66 @@ NHV_API int nhv_silu_mul(int dtype, void* out, const void* gate_up, int n_rows, 
   return 0;
 }
 
+// ---------------------------------------------------------------- gelu_tanh(gate) * up
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); same layout as SiLU(gate) * up above.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void gelu_tanh_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+  pdl_prologue();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter;
+    const int c = (int)(i - t * inter);
+    const float g = to_f32<T>(gate_up[t * 2 * inter + c]);
+    const float u = to_f32<T>(gate_up[t * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(gelu_tanh_f(g) * u);
+  }
+}
+
+__global__ void gelu_tanh_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
+                                            int inter8, size_t total8) {
+  pdl_prologue();
+  const uint4* in = reinterpret_cast<const uint4*>(gate_up);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter8;
+    const size_t a = t * 2 * inter8 + (i - t * inter8);
+    const uint4 gv = in[a], uv = in[a + inter8];
+    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv);
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv);
+    uint4 ov;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = __float2bfloat16_rn(gelu_tanh_f(__bfloat162float(g[k])) * __bfloat162float(u[k]));
+    reinterpret_cast<uint4*>(out)[i] = ov;
+  }
+}
+
+NHV_API int nhv_gelu_tanh_mul(int dtype, void* out, const void* gate_up, int n_rows, int inter, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NHV_REQUIRE(n_rows > 0 && inter > 0, "gelu_tanh_mul: bad sizes");
+  const size_t total = (size_t)n_rows * inter;
+  const int threads = 256;
+  if (dtype == NHV_BF16 && inter % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)gate_up % 16 == 0)) {
+    const size_t total8 = total / 8;
+    const int blocks = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
+    nhv_launch(gelu_tanh_mul_bf16x8_kernel, blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
+               inter / 8, total8);
+  } else {
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == NHV_F32)
+      nhv_launch(gelu_tanh_mul_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)gate_up, inter, total);
+    else if (dtype == NHV_BF16)
+      nhv_launch(gelu_tanh_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out,
+                 (const __nv_bfloat16*)gate_up, inter, total);
+    else
+      NHV_REQUIRE(false, "gelu_tanh_mul: unknown dtype %d", dtype);
+  }
+  NHV_CHECK_LAUNCH("gelu_tanh_mul");
+  return 0;
+}
+
 // ---------------------------------------------------------------- storage type -> fp32 rows
 template <typename T>
 __global__ void to_f32_kernel(float* __restrict__ out, const T* __restrict__ x, size_t total) {

@@ -1,0 +1,109 @@
+// Short causal convolution over time, one filter per channel, with SiLU, for packed steps of several requests.
+//
+//   y[t, c] = silu(bias[c] + sum_{j < K} w[c, j] * x[t - (K - 1) + j, c])
+//
+// where t counts within the request: inputs before the request's first token are zero, and inputs before this
+// step's portion come from the request's state, which holds its last K - 1 inputs (fp32, [slot][K - 1][C], oldest
+// first).  A first kernel computes all outputs (reading the old state), a second one moves the state on; a
+// request with q_start == 0 starts from zeros whatever its slot held.  Requests without a slot (slot < 0: the
+// idle entries that pad a captured batch) read zeros and write nothing.
+#include "nhv_common.cuh"
+
+constexpr int SC_MAX_TAPS = 8;
+constexpr int SC_TOKENS = 8;        // tokens per block of the output kernel
+
+template <typename T>
+__global__ void short_conv_silu_kernel(T* __restrict__ y, int y_stride, const T* __restrict__ x, int x_stride,
+                                       const T* __restrict__ w, const T* __restrict__ bias,
+                                       const float* __restrict__ state, long state_stride,
+                                       const int* __restrict__ cu_q, const int* __restrict__ q_start,
+                                       const int* __restrict__ slots, int n_seqs, int n_tokens, int C, int K) {
+  pdl_prologue();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t0 = blockIdx.x * SC_TOKENS;
+  if (c >= C || t0 >= n_tokens) return;
+  float wk[SC_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < SC_MAX_TAPS; ++j) wk[j] = j < K ? to_f32<T>(w[(size_t)c * K + j]) : 0.f;
+  const float b = bias ? to_f32<T>(bias[c]) : 0.f;
+  // the request of the tile's first token (binary search over the starts), then walk on
+  int lo = 0, hi = n_seqs - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_q[mid] <= t0) lo = mid; else hi = mid - 1;
+  }
+  int s = lo;
+  const int t_end = min(t0 + SC_TOKENS, n_tokens);
+  for (int t = t0; t < t_end; ++t) {
+    while (s + 1 < n_seqs && cu_q[s + 1] <= t) ++s;
+    const int i = t - cu_q[s];                      // index within this step's portion
+    const int slot = slots[s];
+    const bool has_past = slot >= 0 && q_start[s] > 0;
+    float acc = b;
+#pragma unroll
+    for (int j = 0; j < SC_MAX_TAPS; ++j) {
+      if (j < K) {
+        const int rel = i - (K - 1) + j;            // input index relative to the portion's first token
+        float v = 0.f;
+        if (rel >= 0) v = to_f32<T>(x[(size_t)(t - (K - 1) + j) * x_stride + c]);
+        else if (has_past) v = state[(size_t)slot * state_stride + (size_t)(K - 1 + rel) * C + c];
+        acc = fmaf(wk[j], v, acc);
+      }
+    }
+    y[(size_t)t * y_stride + c] = from_f32<T>(acc / (1.0f + expf(-acc)));
+  }
+}
+
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state,
+                                        long state_stride, const int* __restrict__ cu_q,
+                                        const int* __restrict__ q_start, const int* __restrict__ slots, int C, int K) {
+  pdl_prologue();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int slot = slots[s];
+  if (c >= C || slot < 0) return;
+  const int first = cu_q[s], n = cu_q[s + 1] - first;
+  const bool has_past = q_start[s] > 0;
+  float* st = state + (size_t)slot * state_stride;
+  float keep[SC_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < SC_MAX_TAPS - 1; ++j) {
+    keep[j] = 0.f;
+    if (j < K - 1) {
+      const int rel = n - (K - 1) + j;              // the input that becomes entry j of the new state
+      if (rel >= 0) keep[j] = to_f32<T>(x[(size_t)(first + rel) * x_stride + c]);
+      else if (has_past) keep[j] = st[(size_t)(K - 1 + rel) * C + c];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < SC_MAX_TAPS - 1; ++j)
+    if (j < K - 1) st[(size_t)j * C + c] = keep[j];
+}
+
+NHV_API int nhv_short_conv_silu(int dtype, void* y, int y_stride, const void* x, int x_stride, const void* w,
+                                const void* bias, float* state, long state_stride, const int* cu_q,
+                                const int* q_start, const int* slots, int n_seqs, int n_tokens, int C, int K,
+                                cudaStream_t stream) {
+  if (n_tokens == 0 || n_seqs == 0) return 0;
+  NHV_REQUIRE(C > 0 && K >= 1 && K <= SC_MAX_TAPS, "short_conv: %d taps are beyond the supported %d", K, SC_MAX_TAPS);
+  NHV_REQUIRE(state && state_stride >= (long)(K - 1) * C, "short_conv: the state holds fewer than (taps - 1) * channels floats");
+  const int threads = 128;
+  dim3 grid((n_tokens + SC_TOKENS - 1) / SC_TOKENS, (C + threads - 1) / threads);
+  dim3 grid2(n_seqs, (C + threads - 1) / threads);
+#define LAUNCH(T)                                                                                                  \
+  do {                                                                                                             \
+    nhv_launch(short_conv_silu_kernel<T>, grid, threads, 0, stream, (T*)y, y_stride, (const T*)x, x_stride,        \
+               (const T*)w, (const T*)bias, (const float*)state, state_stride, cu_q, q_start, slots, n_seqs,       \
+               n_tokens, C, K);                                                                                    \
+    if (K > 1)                                                                                                     \
+      nhv_launch(short_conv_state_kernel<T>, grid2, threads, 0, stream, (const T*)x, x_stride, state, state_stride, \
+                 cu_q, q_start, slots, C, K);                                                                      \
+  } while (0)
+  if (dtype == NHV_F32) LAUNCH(float);
+  else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
+  else NHV_REQUIRE(false, "short_conv: unknown dtype %d", dtype);
+#undef LAUNCH
+  NHV_CHECK_LAUNCH("short_conv");
+  return 0;
+}

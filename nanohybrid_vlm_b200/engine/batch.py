@@ -182,7 +182,7 @@ class BatchBuilder:
                 firsts.append(it.tokens[0])
                 slots_state.append(-1 if req.state_slot is None else req.state_slot)
                 lp, off = divmod(start, ps)
-                stamp = (req.serial, len(req.tables[0]))     # a request that was given up and came back is another record
+                stamp = (req.serial, len(req.tables[0]) if req.tables else 0)     # a request that was given up and came back is another record
                 new_rows[s] = stamp
                 same = keep and not self._windows and old_rows[s] == stamp
                 for g in range(self.n_groups):

@@ -8,6 +8,8 @@ nanovllm/engine/model_runner.py (init :39-258, cache sizing :650-916, run :2017-
 """
 from __future__ import annotations
 
+from dataclasses import replace
+
 import torch
 
 from ..cache import CacheLayout, CacheManager, CacheStorage
@@ -44,6 +46,9 @@ class ModelRunner:
         torch.cuda.set_device(self.device)
         self.dtype = config.dtype
         spec = config.architecture.build_spec(config.model_config)
+        if spec.max_position > config.max_model_len:
+            # tables indexed by position are built for the positions this engine can reach, not for all a model allows
+            spec = replace(spec, max_position=config.max_model_len)
         self.model = CausalLM(spec, self.dtype, self.device)
         self.model.profile_ranges = bool(config.profile_ranges)
         if random_weights_seed is None:
@@ -57,8 +62,10 @@ class ModelRunner:
         self.page_size = config.kvcache_block_size
         self.max_pages_per_seq = -(-config.max_model_len // self.page_size)
         num_slots = config.num_state_slots
-        if num_slots < 0:
-            num_slots = config.max_num_seqs if self.layout.needs_state_slots else 0
+        if not self.layout.needs_state_slots:
+            num_slots = 0
+        elif num_slots < 0:
+            num_slots = config.max_num_seqs
         num_pages = self._size_pools(num_slots)
         config.num_kvcache_blocks, config.num_state_slots = num_pages, num_slots
         counts = [num_pages] * len(self.layout.groups)

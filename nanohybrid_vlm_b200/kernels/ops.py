@@ -92,6 +92,185 @@ def silu_mul(out, gate_up) -> None:
     call("nhv_silu_mul", dtype_code(out), out.data_ptr(), gate_up.data_ptr(), out.numel() // inter, inter, stream_ptr())
 
 
+def gelu_tanh_mul(out, gate_up) -> None:
+    """out = gelu_tanh(gate) * up for gate_up [n, 2 * inter] with the gate in the first half of each row."""
+    _need_cuda(out, gate_up)
+    _contig("out", out); _contig("gate_up", gate_up)
+    inter = gate_up.shape[-1] // 2
+    assert gate_up.shape[-1] == 2 * inter and out.shape[-1] == inter and out.dtype == gate_up.dtype
+    call("nhv_gelu_tanh_mul", dtype_code(out), out.data_ptr(), gate_up.data_ptr(), out.numel() // inter, inter, stream_ptr())
+
+
+def embed_scaled_f32(out, table, ids, scale: float) -> None:
+    """out [T, width] float32 = table[ids] * scale: the start of a residual stream kept in 32-bit."""
+    _need_cuda(out, table, ids)
+    _contig("out", out); _contig("table", table)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and out.shape[1] == table.shape[1]
+    call("nhv_embed_scaled_f32", dtype_code(table), out.data_ptr(), table.data_ptr(), ids.data_ptr(), ids.numel(),
+         table.shape[1], table.shape[0], float(scale), stream_ptr())
+
+
+def rmsnorm_stream(out, stream, weight, eps: float, addends=(), rows=None, write_stream: bool = True,
+                   weight_offset: float = 0.0) -> None:
+    """The norm over a float32 residual stream [T, width]: s = stream[src] + sum(coef * tensor[src]) in 32-bit over up
+    to three ``addends`` (tensor in the storage type, coef), written back to the stream unless ``rows`` gathers, and
+    out[r] = s / rms(s) * (weight + weight_offset) rounded once to the storage type; src = rows[r] or r."""
+    tensors = [t for t, _ in addends]
+    _need_cuda(out, stream, weight, rows, *tensors)
+    _contig("out", out); _contig("stream", stream)
+    width = stream.shape[-1]
+    assert stream.dtype == torch.float32 and weight.numel() == width and weight.dtype == out.dtype
+    if len(addends) > 3:
+        raise KernelError("the stream norm adds at most three tensors")
+    for t in tensors:
+        _contig("addend", t)
+        assert t.shape == stream.shape and t.dtype == out.dtype
+    n_rows = rows.numel() if rows is not None else stream.numel() // width
+    assert out.numel() == n_rows * width and (rows is None or rows.dtype == torch.int32)
+    ptrs = [t.data_ptr() for t in tensors] + [None] * (3 - len(tensors))
+    coefs = [float(c) for _, c in addends] + [0.0] * (3 - len(tensors))
+    call("nhv_rmsnorm_stream", dtype_code(out), out.data_ptr(), *ptrs, *coefs, stream.data_ptr(), weight.data_ptr(),
+         _ptr(rows), n_rows, width, float(eps), int(bool(write_stream and tensors and rows is None)),
+         float(weight_offset), stream_ptr())
+
+
+def scaled_sum(out, a, b, ca: float, cb: float) -> None:
+    """out = ca * a + cb * b elementwise (sums in 32-bit)."""
+    _need_cuda(out, a, b)
+    _contig("out", out); _contig("a", a); _contig("b", b)
+    assert out.shape == a.shape == b.shape and out.dtype == a.dtype == b.dtype
+    call("nhv_scaled_sum", dtype_code(out), out.data_ptr(), a.data_ptr(), b.data_ptr(), float(ca), float(cb), out.numel(),
+         stream_ptr())
+
+
+def short_conv_silu(out, x, weight, bias, state, batch) -> None:
+    """out [T, C] = silu(causal convolution over time of x [T, C] (a view with unit column stride) with weight [C, K]
+    (+ bias)); ``state`` [slots, (K - 1) * C] float32 holds each request's last K - 1 inputs and is moved on."""
+    _need_cuda(out, x, weight, bias, state)
+    C, K = weight.shape
+    assert x.dim() == 2 and x.shape[1] == C and x.stride(1) == 1 and out.shape == x.shape and out.stride(1) == 1
+    assert out.dtype == x.dtype == weight.dtype and weight.is_contiguous() and state.dtype == torch.float32
+    assert state.dim() == 2 and state.stride(1) == 1 and (bias is None or (bias.dtype == x.dtype and bias.numel() == C))
+    call("nhv_short_conv_silu", dtype_code(x), out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), weight.data_ptr(),
+         _ptr(bias), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+         batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
+
+
+def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int, dv: int) -> None:
+    """The gated delta rule over the step's tokens.  qkv [T, 2*G*d + H*dv] (q, k, v after their convolutions), ba
+    [T, 2*H] float32 (inputs of beta's sigmoid, then of the decay's softplus), a_log / dt_bias [H] float32, state
+    [slots, H*dv*d] float32 -> o [T, H*dv] float32 (before its norm and gate)."""
+    _need_cuda(o, qkv, ba, a_log, dt_bias, state)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == 2 * G * d + H * dv
+    assert o.dtype == ba.dtype == a_log.dtype == dt_bias.dtype == state.dtype == torch.float32
+    assert o.is_contiguous() and o.shape == (T, H * dv) and ba.is_contiguous() and ba.shape == (T, 2 * H)
+    dev = qkv.device
+    qn = torch.empty(T * G * d * 2, dtype=torch.float32, device=dev)
+    gates = torch.empty(T * H * 2, dtype=torch.float32, device=dev)
+    call("nhv_delta_rule", dtype_code(qkv), o.data_ptr(), qkv.data_ptr(), qkv.stride(0), ba.data_ptr(), a_log.data_ptr(),
+         dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qn.data_ptr(), qn.data_ptr() + 4 * T * G * d,
+         gates.data_ptr(), gates.data_ptr() + 4 * T * H, batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+         batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, stream_ptr())
+
+
+def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: int, N: int, G: int) -> None:
+    """The Mamba-2 recurrence over the step's tokens.  xbc [T, H*P + 2*G*N] (x, B, C after the convolution), dt_raw
+    [T, H] float32 (before bias and softplus), state [slots, H*P*N] float32 -> y [T, H*P] float32."""
+    _need_cuda(y, xbc, dt_raw, dt_bias, a_log, d_skip, state)
+    T = xbc.shape[0]
+    assert xbc.stride(1) == 1 and xbc.shape[1] == H * P + 2 * G * N and dt_raw.stride(1) == 1 and dt_raw.shape == (T, H)
+    assert y.dtype == dt_raw.dtype == dt_bias.dtype == a_log.dtype == d_skip.dtype == state.dtype == torch.float32
+    assert y.is_contiguous() and y.shape == (T, H * P)
+    call("nhv_ssd_scan", dtype_code(xbc), y.data_ptr(), xbc.data_ptr(), xbc.stride(0), dt_raw.data_ptr(), dt_raw.stride(0),
+         dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(),
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, P, N, G, stream_ptr())
+
+
+def gated_rmsnorm(out, y, z, weight, n_groups: int, eps: float, gate_first: bool) -> None:
+    """y [T, n_groups * size] float32, gate z [T, same] (a view with unit column stride), weight of any length that
+    divides the row (indexed by column mod its length).  gate_first: out = unit_rms(y * silu(z)) * weight per group;
+    else out = unit_rms(y) * weight * silu(z)."""
+    _need_cuda(out, y, z, weight)
+    T, width = y.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and width % n_groups == 0
+    assert z.shape == y.shape and z.stride(1) == 1 and out.shape == y.shape and out.stride(1) == 1
+    assert out.dtype == z.dtype == weight.dtype and width % weight.numel() == 0
+    call("nhv_gated_rmsnorm", dtype_code(out), out.data_ptr(), out.stride(0), y.data_ptr(), z.data_ptr(), z.stride(0),
+         weight.data_ptr(), weight.numel(), T, n_groups, width // n_groups, float(eps), int(bool(gate_first)), stream_ptr())
+
+
+def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rotary_dim: int, nq: int, nkv: int, dk: int,
+                    dv: int, eps: float | None) -> None:
+    """qkv [T, nq*dk + nkv*dk + nkv*dv] -> q_out [T, nq*dk] (rotated, then scaled to unit root mean square; eps None:
+    no norm) and K / V rows in kv_pages [pages, 2, nkv, page_size, row] at slot_mapping.  kv_pages None: queries only."""
+    _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin)
+    assert qkv.stride(-1) == 1 and q_out.stride(-1) == 1 and qkv.dim() == 2 and q_out.dim() == 2
+    n_tokens = qkv.shape[0]
+    if kv_pages is not None:
+        _contig("kv_pages", kv_pages)
+        n_pages, two, h, page_size, row = kv_pages.shape
+        assert two == 2 and h == nkv and row >= max(dk, dv) and kv_pages.dtype == qkv.dtype
+        assert slot_mapping.dtype == torch.int32 and slot_mapping.numel() >= n_tokens
+    else:
+        n_pages, page_size, row = 0, 0, max(dk, dv)
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == rotary_dim
+        assert positions.dtype == torch.int32
+    call("nhv_rope_norm_store", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), q_out.data_ptr(), q_out.stride(0),
+         _ptr(kv_pages), _ptr(slot_mapping), _ptr(positions), _ptr(cos_sin), int(rotary_dim),
+         0 if cos_sin is None else cos_sin.shape[0], n_tokens, nq, nkv, dk, dv, row, page_size, n_pages,
+         -1.0 if eps is None else float(eps), stream_ptr())
+
+
+def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_tokens: int, nq: int, nkv: int,
+                        dk: int, dv: int, scale: float, sinks=None, window: int = 0) -> None:
+    """Causal attention of this step's tokens over the pages with key heads of dk and value heads of dv elements:
+    q [T, nq*dk] -> out [T, nq*dv].  ``sinks`` [nq] float32: a term exp(sink) in each head's softmax denominator."""
+    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks)
+    _contig("kv_pages", kv_pages)
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and out.dtype == q.dtype == kv_pages.dtype
+    n_pages, two, h, page_size, row = kv_pages.shape
+    assert two == 2 and h == nkv and row >= max(dk, dv)
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq)
+    call("nhv_attention_simt_ex", dtype_code(q), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
+         kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(),
+         n_seqs, n_tokens, nq, nkv, dk, dv, row, page_size, n_pages, int(window), float(scale), _ptr(sinks), stream_ptr())
+
+
+def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, dv: int, scale: float, sinks=None,
+                   window: int = 0) -> None:
+    """Attention of the step's tokens over the cache for layers with a sink and / or value heads of another size
+    than their key heads: picks the kernel for the dtype and sizes."""
+    attention_sink_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
+                        nq, nkv, dk, dv, scale, sinks, window)
+
+
+def linear_f32(out, x, weight) -> None:
+    """out[M,N] float32 = x[M,K] @ weight[N,K]^T with the 32-bit sums kept (no rounding to the storage type on the
+    way): small projections whose results enter a recurrence or a softmax, and heads that return exact logits.
+    float32 operands run the fixed-order kernel; bfloat16 operands the library product with a float32 result."""
+    _need_cuda(out, x, weight)
+    _contig("out", out); _contig("weight", weight)
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype == weight.dtype and out.dtype == torch.float32
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and out.shape == (M, N)
+    if x.dtype == torch.float32:
+        call("nhv_gemm_nt_simt", F32, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 0,
+             stream_ptr())
+    elif N * K <= LINEAR_F32_SIMT_LIMIT or not x.is_contiguous():
+        call("nhv_gemm_nt_simt", BF16, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 1,
+             stream_ptr())
+    else:
+        library.LAUNCHES += 1
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+
+
+LINEAR_F32_SIMT_LIMIT = 1 << 19     # weight elements up to which the fixed-order CUDA-core product takes a bfloat16 matrix
+
+
 def to_f32(out, x) -> None:
     _need_cuda(out, x)
     _contig("out", out); _contig("x", x)

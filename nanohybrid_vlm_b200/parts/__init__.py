@@ -1,8 +1,10 @@
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register the built-in parts)
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block, BuildEnv, CacheView, Embedding,
-                   FeedForward, FixedStateNeed, Head, Mixer, Norm, PagedKVNeed, Part, PositionEncoding)
+from . import (attention, block, delta_rule, embedding, feed_forward, norm, parallel_mixer, position,  # noqa: F401
+               sink_attention, state_space)    # (importing registers the built-in parts)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block, BuildEnv, CacheView, CompositeNeed,
+                   Embedding,
+                   FeedForward, FixedStateNeed, Head, Mixer, Norm, PagedKVNeed, Part, Pending, PositionEncoding)
 from .spec import LayerRun, LayerSpec, ModelSpec, ParamDecl, PartSpec, PartUse, Source, part
 
-__all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "Block", "BuildEnv", "CacheView",
-           "Embedding", "FeedForward", "FixedStateNeed", "Head", "Mixer", "Norm", "PagedKVNeed", "Part", "PositionEncoding",
+__all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS", "Block", "BuildEnv", "CacheView", "CompositeNeed",
+           "Embedding", "FeedForward", "FixedStateNeed", "Head", "Mixer", "Norm", "PagedKVNeed", "Part", "Pending", "PositionEncoding",
            "LayerRun", "LayerSpec", "ModelSpec", "ParamDecl", "PartSpec", "PartUse", "Source", "part"]

@@ -52,10 +52,17 @@ BLOCKS = Registry("block arrangement")
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every token (or of the last ``window`` tokens) in pages."""
+    """Keys and values of every token (or of the last ``window`` tokens) in pages.  ``v_head_dim``: the size of a
+    value head where it differs from a key head's; a page row then has room for the larger of the two and each
+    kind uses its leading elements."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
+
+    @property
+    def row_dim(self) -> int:
+        return max(self.head_dim, self.v_head_dim or self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -63,6 +70,13 @@ class FixedStateNeed:
     """A tensor of fixed shape per live request (``dtype``: "float32" or "model")."""
     shape: tuple[int, ...]
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class CompositeNeed:
+    """Several things kept by one mixer (a mixer made of mixers, or one with pages and a state): the run's
+    :class:`CacheView` then has one child view per entry, in this order."""
+    parts: tuple
 
 
 class BuildEnv:
@@ -115,15 +129,30 @@ class CacheView:
     reads from), ``tables`` the step's block tables and slot mapping for the run's group,
     ``writes`` False if the run must not store keys and values.
     Fixed state: ``state`` [num_slots, *shape]; the step's slots are ``batch.state_slots``.
+    Composite need: ``children``, one view per entry of the need.
     """
     pages: torch.Tensor | None = None
     tables: Any = None
     writes: bool = True
     state: torch.Tensor | None = None
+    children: tuple = ()
+
+
+@dataclass
+class Pending:
+    """Sub-block outputs that are not yet added to a float32 residual stream: the stream becomes
+    stream + sum(coef * tensor) over ``terms`` ((tensor in the model's dtype, coef), ...), summed in 32-bit inside the
+    next norm.  Blocks that keep their stream in float32 hand this on in place of a hidden tensor."""
+    terms: tuple = ()
 
 
 class Mixer(Part):
-    def cache_need(self) -> PagedKVNeed | FixedStateNeed | None:
+    def forward_terms(self, x: torch.Tensor, batch, cache: "CacheView") -> tuple:
+        """The mixer's output as a weighted sum ((tensor, coef), ...) that the caller may add term by term in 32-bit
+        instead of receiving one rounded tensor.  Default: the one tensor of ``forward``."""
+        return ((self.forward(x, batch, cache), 1.0),)
+
+    def cache_need(self) -> "PagedKVNeed | FixedStateNeed | CompositeNeed | None":
         return None
 
     def forward(self, x: torch.Tensor, batch, cache: CacheView) -> torch.Tensor:
@@ -140,8 +169,9 @@ class Norm(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
-    def forward_add(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        """residual += x (in place, fp32 sum rounded once); returns norm of the unrounded sum."""
+    def forward_add(self, x, residual: torch.Tensor) -> torch.Tensor:
+        """residual += x (in place, fp32 sum rounded once); returns norm of the unrounded sum.  ``x`` may be a
+        :class:`Pending` over a float32 ``residual``: the weighted terms are added in 32-bit."""
         raise NotImplementedError
 
     def forward_add_rows(self, x: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

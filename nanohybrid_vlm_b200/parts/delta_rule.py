@@ -1,0 +1,82 @@
+"""The gated delta rule mixer.
+
+Parameters: ``num_heads`` (value heads H), ``num_qk_heads`` (G: value head h uses q/k head h // (H / G)),
+``head_dim`` (d of q and k), ``v_head_dim`` (dv), ``conv`` (taps), ``eps`` (of the output norm).
+
+q, k [G d] and v [H dv] each pass a causal convolution per channel (no bias) and SiLU; q and k become unit vectors
+per head (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.  beta = sigmoid(b(x)), one per head;
+g = exp(-exp(A_log) softplus(a(x) + dt_bias)).  Per head, S [d, dv]: S <- g S; u = beta (v - S^T k);
+S <- S + k u^T; o = S^T q (the read-out sees the current token's write).  Each head's o is divided by its root mean
+square over dv, multiplied by the weight ``norm`` [dv] (shared by the heads) and by silu(gate(x)); then the output
+projection.
+
+Tensors: ``qkvg`` [2 G d + 2 H dv, width] packed from the checkpoint's ``q``, ``k``, ``v``, ``g``; ``ba`` [2 H, width]
+from ``b``, ``a``; ``conv`` [2 G d + H dv, taps] from ``q.conv``, ``k.conv``, ``v.conv``; ``A_log``, ``dt_bias`` [H]
+(float32); ``norm`` [dv]; ``o`` [width, H dv].  Per request the mixer keeps the convolutions' last taps - 1 inputs and
+S, both in float32.  beta, the decay, the unit vectors, the recurrence and the output norm are 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import MIXERS, CompositeNeed, FixedStateNeed, Mixer
+from .spec import ParamDecl, Source
+
+
+class GatedDeltaRule(Mixer):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.H = int(spec["num_heads"])
+        self.G = int(spec.get("num_qk_heads") or self.H)
+        self.d = int(spec["head_dim"])
+        self.dv = int(spec.get("v_head_dim") or self.d)
+        self.taps = int(spec["conv"])
+        self.eps = float(spec["eps"])
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads do not divide into {self.G} q/k heads")
+        self.qk_size, self.v_size = self.G * self.d, self.H * self.dv
+        self.conv_channels = 2 * self.qk_size + self.v_size
+
+    def params(self):
+        W = self.env.hidden_size
+        qk, v, C = self.qk_size, self.v_size, self.conv_channels
+        return [
+            ParamDecl("qkvg", (C + v, W), sources=(Source("q", 0, qk), Source("k", qk, qk), Source("v", 2 * qk, v),
+                                                    Source("g", C, v))),
+            ParamDecl("ba", (2 * self.H, W), sources=(Source("b", 0, self.H), Source("a", self.H, self.H))),
+            ParamDecl("conv", (C, self.taps), sources=(Source("q.conv", 0, qk), Source("k.conv", qk, qk),
+                                                       Source("v.conv", 2 * qk, v))),
+            ParamDecl("A_log", (self.H,), init="zeros_noise", storage="float32"),
+            ParamDecl("dt_bias", (self.H,), init="zeros_noise", storage="float32"),
+            ParamDecl("norm", (self.dv,), init="norm"),
+            ParamDecl("o", (W, v)),
+        ]
+
+    def cache_need(self):
+        return CompositeNeed((FixedStateNeed(((self.taps - 1) * self.conv_channels,)),
+                              FixedStateNeed((self.H * self.dv * self.d,))))
+
+    def streamed_weights(self):
+        return [(self.w_qkvg, 0), (self.w_o, 0)]
+
+    def forward(self, x, batch, cache):
+        T = x.shape[0]
+        C = self.conv_channels
+        conv_state, rule_state = cache.children[0].state, cache.children[1].state
+        proj = self.new(T, C + self.v_size)
+        ops.linear(proj, x, self.w_qkvg)
+        ba = self.new(T, 2 * self.H, dtype=torch.float32)
+        ops.linear_f32(ba, x, self.w_ba)
+        qkv = self.new(T, C)
+        ops.short_conv_silu(qkv, proj[:, :C], self.w_conv, None, conv_state, batch)
+        o = self.new(T, self.v_size, dtype=torch.float32)
+        ops.delta_rule(o, qkv, ba, self.w_A_log, self.w_dt_bias, rule_state, batch, self.G, self.H, self.d, self.dv)
+        gated = self.new(T, self.v_size)
+        ops.gated_rmsnorm(gated, o, proj[:, C:], self.w_norm, self.H, self.eps, gate_first=False)
+        out = self.new(T, self.env.hidden_size)
+        ops.linear(out, gated, self.w_o)
+        return out
+
+
+MIXERS.register("gated_delta_rule", GatedDeltaRule)

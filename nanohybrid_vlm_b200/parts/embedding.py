@@ -2,6 +2,12 @@
 
 The head takes only the rows whose logits are wanted and returns them in fp32.  A tied head
 owns no tensor: it is given the embedding's table.
+
+Embedding parameters: ``vocab_size``, ``scale`` (a factor on the looked-up rows, default none), ``stream`` ("model":
+rows in the model's dtype; "float32": rows in 32-bit, for blocks that keep their residual stream in float32),
+``source`` (the checkpoint's name of the table, default "weight").  Head parameters: ``vocab_size``, ``tied``,
+``exact`` (True: the 32-bit sums of the product are the logits; False: rounded to the model's dtype first and then
+widened, as the reference's head does).
 """
 from __future__ import annotations
 
@@ -9,18 +15,29 @@ import torch
 
 from ..kernels import ops
 from .base import EMBEDDINGS, HEADS, Embedding, Head
-from .spec import ParamDecl
+from .spec import ParamDecl, Source
 
 
 class TokenEmbedding(Embedding):
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab_size"])
+        self.scale = spec.get("scale")
+        self.stream = spec.get("stream", "model")
+        self.source = spec.get("source", "weight")
+        if self.stream not in ("model", "float32"):
+            raise ValueError(f"an embedding's stream is 'model' or 'float32', not {self.stream!r}")
+        if self.scale is not None and self.stream != "float32":
+            raise ValueError("a scaled embedding writes a float32 stream")
 
     def params(self):
-        return [ParamDecl("weight", (self.vocab, self.env.hidden_size))]
+        return [ParamDecl("weight", (self.vocab, self.env.hidden_size), sources=(Source(self.source, 0, self.vocab),))]
 
     def forward(self, token_ids, batch=None):
+        if self.stream == "float32":
+            out = self.new(token_ids.numel(), self.env.hidden_size, dtype=torch.float32)
+            ops.embed_scaled_f32(out, self.w_weight, token_ids, 1.0 if self.scale is None else float(self.scale))
+            return out
         out = self.new(token_ids.numel(), self.env.hidden_size)
         ops.embed(out, self.w_weight, token_ids)
         return out
@@ -31,6 +48,7 @@ class LMHead(Head):
         super().__init__(spec, env)
         self.vocab = int(spec["vocab_size"])
         self.tied = bool(spec.get("tied", False))
+        self.exact = bool(spec.get("exact", False))
 
     def params(self):
         return [] if self.tied else [ParamDecl("weight", (self.vocab, self.env.hidden_size))]
@@ -39,10 +57,13 @@ class LMHead(Head):
         self.w_weight = embedding.w_weight
 
     def streamed_weights(self):
-        return [(self.w_weight, 1)]
+        return [] if self.exact else [(self.w_weight, 1)]
 
     def forward(self, rows_hidden):
         logits = self.new(rows_hidden.shape[0], self.vocab, dtype=torch.float32)
+        if self.exact:
+            ops.linear_f32(logits, rows_hidden, self.w_weight)
+            return logits
         ops.linear(logits, rows_hidden, self.w_weight)
         return logits
 

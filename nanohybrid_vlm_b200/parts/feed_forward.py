@@ -39,4 +39,40 @@ class SwiGLU(FeedForward):
         return y
 
 
+class GatedMLP(FeedForward):
+    """down(act(gate(x)) * up(x)) with a choice of activation.  Parameters: ``intermediate_size``, ``activation``
+    ("silu" or "gelu_tanh"), ``names`` (the checkpoint's names of the gate, up and down matrices; default
+    ("gate", "up", "down")).  Tensors: ``gate_up`` [2 I, width], rows gate then up; ``down`` [width, I]."""
+    ACTIVATIONS = {"silu": "silu_mul", "gelu_tanh": "gelu_tanh_mul"}
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.inter = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {self.activation!r}; known: {sorted(self.ACTIVATIONS)}")
+        self.names = tuple(spec.get("names", ("gate", "up", "down")))
+
+    def params(self):
+        H, I = self.env.hidden_size, self.inter
+        gate, up, down = self.names
+        return [ParamDecl("gate_up", (2 * I, H), sources=(Source(gate, 0, I), Source(up, I, I))),
+                ParamDecl("down", (H, I), sources=(Source(down, 0, H),))]
+
+    def streamed_weights(self):
+        return [(self.w_gate_up, 2 if self.activation == "silu" else 0), (self.w_down, 0)]
+
+    def forward(self, x, batch):
+        T = x.shape[0]
+        act = self.new(T, self.inter)
+        if self.activation != "silu" or not ops.swiglu_first_half(act, x, self.w_gate_up):
+            gate_up = self.new(T, 2 * self.inter)
+            ops.linear(gate_up, x, self.w_gate_up)
+            getattr(ops, self.ACTIVATIONS[self.activation])(act, gate_up)
+        y = self.new(T, self.env.hidden_size)
+        ops.linear(y, act, self.w_down)
+        return y
+
+
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("gated_mlp", GatedMLP)

@@ -30,9 +30,51 @@ class RotaryTable(PositionEncoding):
         return self.table, self.rotary_dim
 
 
+class BandedRotaryTable(PositionEncoding):
+    """Rotary angles whose frequencies are rescaled by wavelength bands (the Llama 3.1 rule).  f_i = theta^(-2i/dims);
+    with wavelength l = 2 pi / f: f stays where l < original / high, becomes f / factor where l > original / low,
+    and in between (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  Parameters: ``theta``,
+    ``rotary_dim``, and optionally ``factor``, ``low``, ``high``, ``original`` (all four or none).  The table covers
+    the positions the engine can reach (``max_position`` of the build environment); frequencies, angles and their
+    cosines are computed in float64 on the host and stored as the nearest float32."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        import math
+        self.rotary_dim = int(spec["rotary_dim"])
+        self.theta = float(spec["theta"])
+        if self.rotary_dim <= 0 or self.rotary_dim % 2:
+            raise ValueError(f"rotary_dim must be positive and even, got {self.rotary_dim}")
+        band = [spec.get(k) for k in ("factor", "low", "high", "original")]
+        if any(b is None for b in band) and not all(b is None for b in band):
+            raise ValueError("frequency bands need factor, low, high and original together")
+        half = self.rotary_dim // 2
+        freqs = []
+        for i in range(half):
+            f = self.theta ** (-2.0 * i / self.rotary_dim)
+            if band[0] is not None:
+                factor, low, high, original = (float(b) for b in band)
+                wavelength = 2.0 * math.pi / f
+                if wavelength > original / low:
+                    f = f / factor
+                elif wavelength >= original / high:
+                    s = (original / wavelength - low) / (high - low)
+                    f = (1.0 - s) * f / factor + s * f
+            freqs.append(f)
+        self.frequencies = torch.tensor(freqs, dtype=torch.float64)
+        self.max_position = int(env.max_position)
+        t = torch.arange(self.max_position, dtype=torch.float64)
+        ang = t[:, None] * self.frequencies[None, :]
+        self.table = torch.cat((ang.cos(), ang.sin()), dim=-1).to(torch.float32).contiguous().to(env.device)
+
+    def rotary(self):
+        return self.table, self.rotary_dim
+
+
 class NoPosition(PositionEncoding):
     """No position signal at all (order then enters only through causality)."""
 
 
 POSITIONS.register("rope", RotaryTable)
+POSITIONS.register("rope_banded", BandedRotaryTable)
 POSITIONS.register("none", NoPosition)
