@@ -87,7 +87,7 @@ NHV_API int nhv_short_conv_silu(int dtype, void* y, int y_stride, const void* x,
                                 cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(C > 0 && K >= 1 && K <= SC_MAX_TAPS, "short_conv: %d taps are beyond the supported %d", K, SC_MAX_TAPS);
-  NHV_REQUIRE(state && state_stride >= (long)(K - 1) * C, "short_conv: the state holds fewer than (taps - 1) * channels floats");
+  NHV_REQUIRE(K == 1 || (state && state_stride >= (long)(K - 1) * C), "short_conv: the state holds fewer than (taps - 1) * channels floats");
   const int threads = 128;
   dim3 grid((n_tokens + SC_TOKENS - 1) / SC_TOKENS, (C + threads - 1) / threads);
   dim3 grid2(n_seqs, (C + threads - 1) / threads);

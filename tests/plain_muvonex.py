@@ -117,6 +117,34 @@ def attention_side(h, w, pre, m, eps, positions):
 
 
 # ---------------------------------------------------------------- state-space side
+def ssd_recurrence(x, B, C, dt_raw, dt_bias, a_log, skip, S0=None):
+    """x [T, heads, P], B and C [T, G, N], dt_raw [T, heads] -> y [T, heads, P] (and the last state with S0 given).
+    Per head: S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + skip x, dt = softplus(dt_raw + dt_bias)."""
+    T, heads, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    dt = softplus(dt_raw + dt_bias)
+    rate = torch.exp(a_log)
+    y = torch.zeros(T, heads, P, dtype=x.dtype)
+    last = torch.zeros(heads, N, P, dtype=x.dtype)
+    for hd in range(heads):
+        g = hd // (heads // G)
+        S = torch.zeros(N, P, dtype=x.dtype) if S0 is None else S0[hd].clone()
+        for t in range(T):
+            S = torch.exp(-rate[hd] * dt[t, hd]) * S + dt[t, hd] * torch.outer(B[t, g], x[t, hd])
+            y[t, hd] = S.T @ C[t, g] + skip[hd] * x[t, hd]
+        last[hd] = S
+    return y if S0 is None else (y, last)
+
+
+def gated_norm(y, z, weight, parts, eps, gate_first):
+    """y, z [T, n]; gate_first: unit_rms(y silu(z)) w in ``parts`` equal parts; else unit_rms(y) w silu(z), w tiled."""
+    T, n = y.shape
+    if gate_first:
+        y = y * silu(z)
+    y = rms_unit(y.view(T, parts, n // parts), eps).reshape(T, n) * weight.repeat(n // weight.numel())
+    return y if gate_first else y * silu(z)
+
+
 def ssd_side(h, w, pre, m, eps):
     heads, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = heads * P
@@ -127,15 +155,7 @@ def ssd_side(h, w, pre, m, eps):
     x = xbc[:, :inner].view(T, heads, P)
     B = xbc[:, inner:inner + G * N].view(T, G, N)
     C = xbc[:, inner + G * N:].view(T, G, N)
-    dt = softplus(dt + w[pre + "dt_bias"])
-    rate = torch.exp(w[pre + "A_log"])
-    y = torch.zeros(T, heads, P, dtype=h.dtype)
-    for hd in range(heads):
-        g = hd // (heads // G)
-        S = torch.zeros(N, P, dtype=h.dtype)
-        for t in range(T):
-            S = torch.exp(-rate[hd] * dt[t, hd]) * S + dt[t, hd] * torch.outer(B[t, g], x[t, hd])
-            y[t, hd] = S.T @ C[t, g] + w[pre + "D"][hd] * x[t, hd]
+    y = ssd_recurrence(x, B, C, dt, w[pre + "dt_bias"], w[pre + "A_log"], w[pre + "D"])
     y = y.reshape(T, inner) * silu(z)
     parts = m["norm_groups"]
     y = rms_unit(y.view(T, parts, inner // parts), eps).reshape(T, inner) * w[pre + "norm"]
@@ -148,6 +168,25 @@ def parallel_mixer(h, w, pre, m, eps, positions):
 
 
 # ---------------------------------------------------------------- gated delta rule
+def delta_recurrence(q, k, v, beta, decay, S0=None):
+    """q, k [T, G, d] (already unit vectors), v [T, H, dv], beta and decay [T, H] -> o [T, H, dv] (and the last
+    state with S0 given).  Per head: S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
+    T, H, dv = v.shape
+    G, d = q.shape[1], q.shape[2]
+    o = torch.zeros(T, H, dv, dtype=v.dtype)
+    last = torch.zeros(H, d, dv, dtype=v.dtype)
+    for hd in range(H):
+        g = hd // (H // G)
+        S = torch.zeros(d, dv, dtype=v.dtype) if S0 is None else S0[hd].clone()
+        for t in range(T):
+            S = decay[t, hd] * S
+            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
+            S = S + torch.outer(k[t, g], u)
+            o[t, hd] = S.T @ q[t, g]
+        last[hd] = S
+    return o if S0 is None else (o, last)
+
+
 def delta_mixer(h, w, pre, m, eps):
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
@@ -158,15 +197,7 @@ def delta_mixer(h, w, pre, m, eps):
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ w[pre + "b"].T)
     decay = torch.exp(-torch.exp(w[pre + "A_log"]) * softplus(h @ w[pre + "a"].T + w[pre + "dt_bias"]))
-    o = torch.zeros(T, H, dv, dtype=h.dtype)
-    for hd in range(H):
-        g = hd // (H // G)
-        S = torch.zeros(d, dv, dtype=h.dtype)
-        for t in range(T):
-            S = decay[t, hd] * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + torch.outer(k[t, g], u)
-            o[t, hd] = S.T @ q[t, g]
+    o = delta_recurrence(q, k, v, beta, decay)
     o = rms_unit(o, eps) * w[pre + "norm"]
     o = o.reshape(T, H * dv) * silu(h @ w[pre + "g"].T)
     return o @ w[pre + "o"].T
