@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload 0.6b|32b      the baseline's other two workloads, through the Python entry point
     python bench.py --breakdown              where a decode step's and a prefill's time goes, by kind of kernel
+    python bench.py --designs                Muvonex beside a Qwen3 of equal size (prefill, decode, time by kind of kernel)
 
 The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 layers, width 4096,
 32/8 heads of 128, feed-forward 12288, vocabulary 151936), bfloat16, random weights, batch 8,
@@ -640,6 +641,172 @@ def bench_reference(args) -> dict:
     }
 
 
+# ---------------------------------------------------------------- two designs side by side
+# Layer sizes that resemble real models: a Muvonex of three delta-rule layers and one parallel layer (attention with a
+# sink beside Mamba-2), repeated, and a Qwen3 of the same width, depth and number of weights per layer.
+DESIGN_SIZES = {
+    "1k": dict(width=1024, heads=8, ff=2816),
+    "2k": dict(width=2048, heads=16, ff=5632),
+    "4k": dict(width=4096, heads=32, ff=11264),
+}
+DESIGN_VOCAB = 32000
+
+
+def muvonex_config(width: int, heads: int, ff: int, layers: int) -> dict:
+    delta = dict(type="delta", mlp=dict(kind="dense", ff=ff),
+                 mixer=dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4))
+    par = dict(type="parallel", mlp=dict(kind="dense", ff=ff), mixer=dict(
+        left=dict(heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5,
+                  rot=dict(base=500000.0, dims=128, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))),
+        right=dict(heads=2 * heads, groups=1, state=128, vdim=64, conv=4, norm_groups=1),
+        left_scale=1.0, right_scale=1.0))
+    return dict(architecture="Muvonex", vocab=DESIGN_VOCAB, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-6),
+                residual_mult=1.0, layers=[par if i % 4 == 3 else delta for i in range(layers)], dtype="bfloat16")
+
+
+def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weights: float) -> dict:
+    """A Qwen3 of this width whose layers hold as many weights as ``layer_weights`` (the feed-forward takes up the
+    difference, rounded to 256)."""
+    attn = width * 128 * (2 * heads + 2 * max(heads // 4, 1))
+    inter = max(256, int(round((layer_weights - attn) / (3 * width) / 256)) * 256)
+    return dict(CONFIG_8B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads,
+                num_key_value_heads=max(heads // 4, 1), intermediate_size=inter, vocab_size=DESIGN_VOCAB,
+                tie_word_embeddings=True)
+
+
+def bench_designs(args) -> dict:
+    """Prefill and decode throughput of Muvonex beside a Qwen3 of equal size, and the time of each kind of kernel in
+    a prefill step (CUDA events around every launch of an eager run) with its share of the measured roofline."""
+    import torch
+
+    from nanohybrid_vlm_b200 import LLM
+    from nanohybrid_vlm_b200.engine import StepItem
+    from nanohybrid_vlm_b200.kernels import ops
+
+    pk = peaks()
+    layers = args.layers if args.layers != FULL_LAYERS else 4
+    T, ctx, page = 4096, 2048, 256
+    kinds = {"linear": "gemm", "linear_f32": "gemm", "swiglu_first_half": "gemm", "rmsnorm": "norm", "rmsnorm_stream": "norm",
+             "qk_norm_rope_store": "rope_store", "rope_norm_store": "rope_store", "attention": "attention",
+             "attention_sink": "attention", "attention_decode_fused": "attention", "silu_mul": "act_mul",
+             "gelu_tanh_mul": "act_mul", "embed": "embed", "embed_scaled_f32": "embed", "short_conv_silu": "short_conv",
+             "delta_rule": "delta_rule", "ssd_scan": "ssd_scan", "gated_rmsnorm": "gated_norm", "sample": "sample"}
+    kinds = {k: v for k, v in kinds.items() if hasattr(ops, k)}
+    stock = {name: getattr(ops, name) for name in kinds}
+    gen = torch.Generator().manual_seed(SEED)
+
+    def run_one(cfg: dict, vocab: int) -> dict:
+        with tempfile.TemporaryDirectory() as d:
+            with open(os.path.join(d, "config.json"), "w") as f:
+                json.dump(cfg, f)
+            llm = LLM(d, random_weights_seed=SEED, kvcache_block_size=page, num_kvcache_blocks=66 * (ctx + page) // page,
+                      max_model_len=max(T, ctx + page), max_num_seqs=64, max_num_batched_tokens=T, seed=SEED,
+                      enforce_eager=args.eager)
+        runner = llm.model_runner
+        weights = sum(bp.decl.shape[0] * bp.decl.shape[1] for bp in runner.model.param_table() if len(bp.decl.shape) == 2)
+        prompt = torch.randint(0, vocab, (T,), generator=gen).tolist()
+        events, depth = [], [0]
+
+        def timed(name, fn):
+            def call(*a, **kw):
+                if depth[0]:
+                    return fn(*a, **kw)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                depth[0] += 1
+                e0.record()
+                try:
+                    return fn(*a, **kw)
+                finally:
+                    e1.record()
+                    depth[0] -= 1
+                    events.append((kinds[name], e0, e1))
+            return call
+
+        def prefill():
+            runner.cache.allocate("pf", T)
+            runner.step([StepItem("pf", prompt, 0, [T - 1])])
+            runner.cache.free("pf")
+
+        for _ in range(max(args.warmup, 3)):
+            prefill()
+        torch.cuda.synchronize()
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            prefill()
+        e1.record()
+        torch.cuda.synchronize()
+        prefill_ms = e0.elapsed_time(e1) / reps
+        for name, fn in stock.items():
+            setattr(ops, name, timed(name, fn))
+        try:
+            for _ in range(reps):
+                prefill()
+            torch.cuda.synchronize()
+        finally:
+            for name, fn in stock.items():
+                setattr(ops, name, fn)
+        by_kind = {}
+        for kind, a, b in events:
+            by_kind[kind] = by_kind.get(kind, 0.0) + a.elapsed_time(b) * 1e3 / reps
+        out = {"weights_m": round(weights / 1e6, 1), "prefill_ms": round(prefill_ms, 3),
+               "prefill_tok_s": round(T / prefill_ms * 1e3),
+               "prefill_us_by_kind": {k: round(v, 1) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])}}
+        gemm_flops = 2.0 * T * (weights - vocab * cfg.get("width", cfg.get("hidden_size")))
+        if "gemm" in by_kind:
+            out["gemm_frac_of_measured_bf16"] = round(gemm_flops / (by_kind["gemm"] * 1e-6) / (pk["bf16_tflops"] * 1e12), 3)
+        for batch in (8, 64):
+            ids = [f"d{batch}_{i}" for i in range(batch)]
+            lens = {}
+            for i in ids:
+                runner.cache.allocate(i, ctx + 1)
+                runner.step([StepItem(i, prompt[:ctx], 0, [])])
+                lens[i] = ctx
+
+            def decode():
+                items = []
+                for i in ids:
+                    runner.cache.allocate(i, lens[i] + 1)
+                    items.append(StepItem(i, [1], lens[i], [0]))
+                    lens[i] += 1
+                runner.run(items, [(0.0, 1, lens[i]) for i in ids])
+
+            for _ in range(max(args.warmup, 3)):
+                decode()
+            torch.cuda.synchronize()
+            steps = min(args.steps, page - 8)
+            e0.record()
+            for _ in range(steps):
+                decode()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            item = 2
+            read = weights * item + sum(runner.layout.page_bytes(page, torch.bfloat16)) * batch * (ctx // page) \
+                + runner.layout.state_bytes_per_slot(torch.bfloat16) * batch * 2
+            out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 3), "tok_s": round(batch / ms * 1e3),
+                                       "hbm_frac_of_measured": round(read / (ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)}
+            for i in ids:
+                runner.cache.free(i)
+        del llm, runner
+        torch.cuda.empty_cache()
+        return out
+
+    results = {}
+    for name in ([args.design_size] if args.design_size != "all" else list(DESIGN_SIZES)):
+        sz = DESIGN_SIZES[name]
+        mcfg = muvonex_config(sz["width"], sz["heads"], sz["ff"], layers)
+        m = run_one(mcfg, DESIGN_VOCAB)
+        layer_weights = (m["weights_m"] * 1e6 - DESIGN_VOCAB * sz["width"]) / layers
+        q = run_one(qwen3_config_of_equal_size(sz["width"], sz["heads"], layers, layer_weights), DESIGN_VOCAB)
+        results[name] = {"muvonex": m, "qwen3": q}
+    return {"designs": results, "layers": layers, "prefill_tokens": T, "decode_context": ctx, "dtype": "bf16",
+            "data": "synthetic (random weights, uniform-random tokens)", "peaks": pk,
+            "how": "CUDA events; prefill: one prompt in one step; decode: the runner's step-and-sample call; by kind: events "
+                   "around every launch of the same prefill (the gaps before a kind's launches count toward it)"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -660,13 +827,18 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
     ap.add_argument("--breakdown", action="store_true",
                     help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
+    ap.add_argument("--designs", action="store_true",
+                    help="Muvonex beside a Qwen3 of equal size: prefill and decode throughput at a few layer sizes; one JSON line")
+    ap.add_argument("--design-size", default="all", choices=["all", *DESIGN_SIZES], help="one size of --designs")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (N=1 only)")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.breakdown:
+    if args.designs:
+        out = bench_designs(args)
+    elif args.breakdown:
         out = bench_breakdown(args)
     elif args.workload != "8b":
         if args.impl == "reference":

@@ -6,11 +6,19 @@
 //   beta_t = sigmoid(b_t),  g_t = exp(-exp(A_log) * softplus(a_t + dt_bias)).
 // Each o_t is then divided by its root mean square over dv, multiplied by a weight [dv] and by silu(gate_t).
 //
-// delta_prepare: one warp per (token, q/k head): the unit vectors in fp32; one thread per (token, head): beta, g.
-// delta_scan:    one block per (request, head, tile of 64 columns of S).  Thread (column j, part p of P = 4) keeps
-//                rows p, p + 4, ... of column j in registers; sums over rows end with two shuffles.  Tokens go
-//                through shared memory in chunks of 16.  It writes o_t in fp32; the norm and the gate follow in
-//                nhv_gated_rmsnorm (state_space.cu).
+// delta_prepare: one warp per (token, q/k head pair): the unit vectors in fp32 and their product k_t . q_t; one
+//                thread per (token, head): beta, g; the values v_t widened to fp32.
+// delta_scan:    the columns of S are independent of one another (column j: u_j = beta (v_j - S_j . k),
+//                S_j += u_j k, o_j = S_j . q), so a block takes (request, head, 16 columns) and a column lives in
+//                the registers of 8 lanes, each with d / 8 rows in groups of 4 (one 16-byte read of k and of q
+//                from shared memory serves 4 rows).  Per token the two sums S_j . k and S_j . q are taken from
+//                the state BEFORE the write, side by side (four partial sums each, then three shuffles), and
+//                  o_j = g S_j . q + u_j (k . q),   S_j <- g S_j + u_j k
+//                which is the read-out after the write, since (g S + k u^T)^T q = g S^T q + u (k . q).  Tokens
+//                reach shared memory by cp.async, 16 at a time, the next 16 while these are worked on.
+// delta_scan_any: the same recurrence for sizes that are no multiple of 4 (no 16-byte copies): 64 columns a
+//                block, 4 lanes a column, plain loads.
+// Both write o_t in fp32; the norm and the gate follow in nhv_gated_rmsnorm (state_space.cu).
 // The state of a slot is stored transposed, [head][dv][d].  A request with q_start == 0 starts from zeros; one
 // without a slot (slot < 0) is skipped and its outputs are cleared.
 #include <math.h>
@@ -24,39 +32,190 @@ constexpr int DR_COLS = 64;         // columns of S per block
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 template <typename T>
-__global__ void delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ beta,
-                                     float* __restrict__ decay, const T* __restrict__ qkv, int qkv_stride,
-                                     const float* __restrict__ ba, const float* __restrict__ a_log,
-                                     const float* __restrict__ dt_bias, int n_tokens, int G, int H, int d) {
+__global__ void delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ kq,
+                                     float* __restrict__ v32, float* __restrict__ beta, float* __restrict__ decay,
+                                     const T* __restrict__ qkv, int qkv_stride, const float* __restrict__ ba,
+                                     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                     int n_tokens, int G, int H, int d, int dv) {
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
-  const long n_vec = (long)n_tokens * 2 * G;
-  if (item < n_vec) {
-    const int t = (int)(item / (2 * G)), hh = (int)(item % (2 * G));       // hh < G: a q head, else a k head
-    const T* src = qkv + (size_t)t * qkv_stride + (size_t)hh * d;
-    float ss = 0.f;
+  const long n_warps = (long)gridDim.x * (blockDim.x >> 5);
+  for (long item = (long)blockIdx.x * (blockDim.x >> 5) + warp; item < (long)n_tokens * G; item += n_warps) {
+    const int t = (int)(item / G), g = (int)(item % G);
+    const T* qs = qkv + (size_t)t * qkv_stride + (size_t)g * d;
+    const T* ks = qs + (size_t)G * d;
+    float sq = 0.f, sk = 0.f;
     for (int c = lane; c < d; c += 32) {
-      const float x = to_f32<T>(src[c]);
-      ss = fmaf(x, x, ss);
+      const float a = to_f32<T>(qs[c]), b = to_f32<T>(ks[c]);
+      sq = fmaf(a, a, sq);
+      sk = fmaf(b, b, sk);
     }
-    ss = warp_sum(ss);
-    float r = 1.0f / sqrtf(ss + 1e-6f);
-    float* dst;
-    if (hh < G) {
-      r *= 1.0f / sqrtf((float)d);
-      dst = qn + ((size_t)t * G + hh) * d;
-    } else {
-      dst = kn + ((size_t)t * G + (hh - G)) * d;
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float rq = 1.0f / sqrtf(sq + 1e-6f) * (1.0f / sqrtf((float)d)), rk = 1.0f / sqrtf(sk + 1e-6f);
+    float dot = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      const float a = to_f32<T>(qs[c]) * rq, b = to_f32<T>(ks[c]) * rk;
+      qn[(size_t)item * d + c] = a;
+      kn[(size_t)item * d + c] = b;
+      dot = fmaf(a, b, dot);
     }
-    for (int c = lane; c < d; c += 32) dst[c] = to_f32<T>(src[c]) * r;
+    dot = warp_sum(dot);
+    if (lane == 0) kq[item] = dot;
   }
-  const long gi = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (gi < (long)n_tokens * H) {
-    const int t = (int)(gi / H), h = (int)(gi % H);
+  const long n_threads = (long)gridDim.x * blockDim.x, me = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (long i = me; i < (long)n_tokens * H; i += n_threads) {
+    const int t = (int)(i / H), h = (int)(i % H);
     const float b = ba[(size_t)t * 2 * H + h], a = ba[(size_t)t * 2 * H + H + h];
-    beta[gi] = 1.0f / (1.0f + expf(-b));
-    decay[gi] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+    beta[i] = 1.0f / (1.0f + expf(-b));
+    decay[i] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+  }
+  if (v32) {
+    const int hv = H * dv;
+    const T* vs = qkv + (size_t)2 * G * d;
+    for (long i = me; i < (long)n_tokens * hv; i += n_threads) {
+      const long t = i / hv;
+      v32[i] = to_f32<T>(vs[(size_t)t * qkv_stride + (i - t * hv)]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- the scan for sizes in steps of 4
+constexpr int DF_COLS = 16;         // columns of S per block
+constexpr int DF_LANES = 8;         // lanes per column
+constexpr int DF_CHUNK = 16;        // tokens per stage
+constexpr int DF_THREADS = DF_COLS * DF_LANES;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// R: rows of a column per lane (a multiple of 4, R * 8 >= d).  qn, kn [T, G, d]; v32 [T, H, dv]; kq [T, G]; all fp32.
+template <int R>
+__global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
+    float* __restrict__ o_out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ kq,
+    const float* __restrict__ v32, const float* __restrict__ beta, const float* __restrict__ decay,
+    float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int G, int H, int d, int dv) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_prologue();
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DF_COLS;
+  const int g = h / (H / G);
+  const int first = cu_q[s], n = cu_q[s + 1] - first;
+  const int slot = slots[s];
+  const int tid = threadIdx.x;
+  const int ncol = min(DF_COLS, dv - col0);            // a multiple of 4
+  if (slot < 0) {
+    for (int i = tid; i < n * ncol; i += DF_THREADS)
+      o_out[((size_t)(first + i / ncol) * H + h) * dv + col0 + i % ncol] = 0.f;
+    return;
+  }
+  const int stage_floats = DF_CHUNK * (2 * d + DF_COLS + 4);
+  const int cl = tid / DF_LANES, part = tid % DF_LANES;
+  const bool live = cl < ncol;
+  const int col = col0 + (live ? cl : 0);
+  float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + col) * d;
+  float S[R];
+  const bool fresh = q_start[s] == 0;
+#pragma unroll
+  for (int j = 0; j < R / 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 4 * (part + DF_LANES * j) + e;
+      S[4 * j + e] = (live && !fresh && i < d) ? st[i] : 0.f;
+    }
+
+  auto fetch = [&](int c0, int stage) {
+    float* qs = smem + stage * stage_floats;           // [CHUNK][d]
+    float* ks = qs + DF_CHUNK * d;                     // [CHUNK][d]
+    float* vs = ks + DF_CHUNK * d;                     // [CHUNK][DF_COLS]
+    float* sc = vs + DF_CHUNK * DF_COLS;               // [CHUNK][4]: decay, beta, k . q
+    const int cn = min(DF_CHUNK, n - c0);
+    const int d4 = d >> 2, c4 = ncol >> 2;
+    for (int i = tid; i < cn * d4; i += DF_THREADS) {
+      const int tt = i / d4, c = i - tt * d4;
+      const size_t row = ((size_t)(first + c0 + tt) * G + g) * d + 4 * c;
+      cp_async16(qs + tt * d + 4 * c, qn + row);
+      cp_async16(ks + tt * d + 4 * c, kn + row);
+    }
+    for (int i = tid; i < cn * c4; i += DF_THREADS) {
+      const int tt = i / c4, c = i - tt * c4;
+      cp_async16(vs + tt * DF_COLS + 4 * c, v32 + ((size_t)(first + c0 + tt) * H + h) * dv + col0 + 4 * c);
+    }
+    for (int i = tid; i < cn * 3; i += DF_THREADS) {
+      const int tt = i / 3, w = i - tt * 3;
+      const size_t tok = first + c0 + tt;
+      cp_async4(sc + tt * 4 + w, w == 0 ? decay + tok * H + h : (w == 1 ? beta + tok * H + h : kq + tok * G + g));
+    }
+  };
+
+  const int n_chunks = (n + DF_CHUNK - 1) / DF_CHUNK;
+  if (n_chunks > 0) fetch(0, 0);
+  cp_async_commit();
+  for (int ci = 0; ci < n_chunks; ++ci) {
+    const int c0 = ci * DF_CHUNK, stage = ci & 1;
+    if (ci + 1 < n_chunks) fetch(c0 + DF_CHUNK, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const float* qs = smem + stage * stage_floats;
+    const float* ks = qs + DF_CHUNK * d;
+    const float* vs = ks + DF_CHUNK * d;
+    const float* sc = vs + DF_CHUNK * DF_COLS;
+    const int cn = min(DF_CHUNK, n - c0);
+    for (int tt = 0; tt < cn; ++tt) {
+      const float gt = sc[tt * 4], bt = sc[tt * 4 + 1], kqt = sc[tt * 4 + 2];
+      float4 kk[R / 4], qq[R / 4];
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const int c = part + DF_LANES * j;
+        if (4 * c < d) {
+          kk[j] = *reinterpret_cast<const float4*>(ks + tt * d + 4 * c);
+          qq[j] = *reinterpret_cast<const float4*>(qs + tt * d + 4 * c);
+        } else {
+          kk[j] = qq[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      float ak[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        ak[0] = fmaf(S[4 * j], kk[j].x, ak[0]);     aq[0] = fmaf(S[4 * j], qq[j].x, aq[0]);
+        ak[1] = fmaf(S[4 * j + 1], kk[j].y, ak[1]); aq[1] = fmaf(S[4 * j + 1], qq[j].y, aq[1]);
+        ak[2] = fmaf(S[4 * j + 2], kk[j].z, ak[2]); aq[2] = fmaf(S[4 * j + 2], qq[j].z, aq[2]);
+        ak[3] = fmaf(S[4 * j + 3], kk[j].w, ak[3]); aq[3] = fmaf(S[4 * j + 3], qq[j].w, aq[3]);
+      }
+      float sk = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq = (aq[0] + aq[1]) + (aq[2] + aq[3]);
+#pragma unroll
+      for (int off = 1; off < DF_LANES; off <<= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, off);
+        sq += __shfl_xor_sync(0xffffffffu, sq, off);
+      }
+      const float u = bt * ((live ? vs[tt * DF_COLS + cl] : 0.f) - gt * sk);
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        S[4 * j] = fmaf(kk[j].x, u, gt * S[4 * j]);
+        S[4 * j + 1] = fmaf(kk[j].y, u, gt * S[4 * j + 1]);
+        S[4 * j + 2] = fmaf(kk[j].z, u, gt * S[4 * j + 2]);
+        S[4 * j + 3] = fmaf(kk[j].w, u, gt * S[4 * j + 3]);
+      }
+      if (live && part == 0) o_out[((size_t)(first + c0 + tt) * H + h) * dv + col] = fmaf(u, kqt, gt * sq);
+    }
+    __syncthreads();                                   // the stage is free for the fetch after next
+  }
+  cp_async_wait<0>();
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < R / 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 4 * (part + DF_LANES * j) + e;
+        if (i < d) st[i] = S[4 * j + e];
+      }
   }
 }
 
@@ -151,41 +310,68 @@ __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_scan_kernel(
   }
 }
 
-// o_out [T, H, dv] fp32.  Scratch given by the caller: qn, kn [T, G, d] and beta, decay [T, H], all fp32.
+// o_out [T, H, dv] fp32.  Scratch given by the caller, all fp32: qn, kn [T, G, d]; kq [T, G]; v32 [T, H, dv]; beta,
+// decay [T, H].
 NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_stride, const float* ba,
                            const float* a_log, const float* dt_bias, float* state, long state_stride, float* qn,
-                           float* kn, float* beta, float* decay, const int* cu_q, const int* q_start,
-                           const int* slots, int n_seqs, int n_tokens, int G, int H, int d, int dv,
+                           float* kn, float* kq, float* v32, float* beta, float* decay, const int* cu_q,
+                           const int* q_start, const int* slots, int n_seqs, int n_tokens, int G, int H, int d, int dv,
                            cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(G > 0 && H > 0 && H % G == 0, "delta_rule: %d heads do not divide into %d q/k heads", H, G);
   NHV_REQUIRE(d > 0 && d <= 256 && dv > 0, "delta_rule: a q/k head of %d is beyond the supported 256", d);
   NHV_REQUIRE(state_stride >= (long)H * d * dv, "delta_rule: the state holds fewer than heads * d * dv floats");
-  const int rows = (d + DR_PARTS - 1) / DR_PARTS;
-  const int threads = DR_COLS * DR_PARTS;
-  const size_t smem = ((size_t)DR_CHUNK * (2 * d + DR_COLS) + 2 * DR_CHUNK) * sizeof(float);
-  const long vec = (long)n_tokens * 2 * G, gates = ((long)n_tokens * H + 31) / 32;
-  const int prep_blocks = (int)(((vec > gates ? vec : gates) + 3) / 4);
-  dim3 grid(n_seqs, H, (dv + DR_COLS - 1) / DR_COLS);
+  const bool fast = d % 4 == 0 && dv % 4 == 0;
+  const long work = (long)n_tokens * (H * dv > 32 * G ? H * dv : 32 * G);
+  const int prep_blocks = (int)(work / 256 + 1 < 148 * 8 ? work / 256 + 1 : 148 * 8);
   const int v_off = 2 * G * d;
+#define PREP(T)                                                                                                      \
+  nhv_launch(delta_prepare_kernel<T>, prep_blocks, 256, 0, stream, qn, kn, kq, fast ? v32 : (float*)nullptr, beta,   \
+             decay, (const T*)qkv, qkv_stride, ba, a_log, dt_bias, n_tokens, G, H, d, dv)
+  if (dtype == NHV_F32) PREP(float);
+  else if (dtype == NHV_BF16) PREP(__nv_bfloat16);
+  else NHV_REQUIRE(false, "delta_rule: unknown dtype %d", dtype);
+#undef PREP
+  if (fast) {
+    const size_t smem = (size_t)2 * DF_CHUNK * (2 * d + DF_COLS + 4) * sizeof(float);
+    dim3 grid(n_seqs, H, (dv + DF_COLS - 1) / DF_COLS);
+#define FAST(R)                                                                                                      \
+  do {                                                                                                               \
+    static bool attr = false;                                                                                        \
+    if (!attr) {                                                                                                     \
+      NHV_CUDA(cudaFuncSetAttribute(delta_scan_fast_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                    (int)((size_t)2 * DF_CHUNK * (2 * 256 + DF_COLS + 4) * sizeof(float))), "delta_rule"); \
+      attr = true;                                                                                                   \
+    }                                                                                                                \
+    nhv_launch(delta_scan_fast_kernel<R>, grid, DF_THREADS, smem, stream, o_out, (const float*)qn, (const float*)kn, \
+               (const float*)kq, (const float*)v32, (const float*)beta, (const float*)decay, state, state_stride,   \
+               cu_q, q_start, slots, G, H, d, dv);                                                                   \
+  } while (0)
+    if (d <= 32) FAST(4);
+    else if (d <= 64) FAST(8);
+    else if (d <= 128) FAST(16);
+    else FAST(32);
+#undef FAST
+  } else {
+    const int rows = (d + DR_PARTS - 1) / DR_PARTS;
+    const size_t smem = ((size_t)DR_CHUNK * (2 * d + DR_COLS) + 2 * DR_CHUNK) * sizeof(float);
+    dim3 grid(n_seqs, H, (dv + DR_COLS - 1) / DR_COLS);
 #define SCAN(T, R)                                                                                                  \
-  nhv_launch(delta_scan_kernel<T, R>, grid, threads, smem, stream, o_out, (const float*)qn, (const float*)kn,       \
+  nhv_launch(delta_scan_kernel<T, R>, grid, DR_COLS * DR_PARTS, smem, stream, o_out, (const float*)qn, (const float*)kn, \
              (const T*)qkv + v_off, qkv_stride, (const float*)beta, (const float*)decay, state, state_stride, cu_q, \
              q_start, slots, G, H, d, dv)
-#define LAUNCH(T)                                                                                                   \
-  do {                                                                                                              \
-    nhv_launch(delta_prepare_kernel<T>, prep_blocks, 128, 0, stream, qn, kn, beta, decay, (const T*)qkv, qkv_stride, \
-               ba, a_log, dt_bias, n_tokens, G, H, d);                                                              \
-    if (rows <= 8) SCAN(T, 8);                                                                                      \
-    else if (rows <= 16) SCAN(T, 16);                                                                               \
-    else if (rows <= 32) SCAN(T, 32);                                                                               \
-    else SCAN(T, 64);                                                                                               \
+#define LAUNCH(T)                          \
+  do {                                     \
+    if (rows <= 8) SCAN(T, 8);             \
+    else if (rows <= 16) SCAN(T, 16);      \
+    else if (rows <= 32) SCAN(T, 32);      \
+    else SCAN(T, 64);                      \
   } while (0)
-  if (dtype == NHV_F32) LAUNCH(float);
-  else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
-  else NHV_REQUIRE(false, "delta_rule: unknown dtype %d", dtype);
+    if (dtype == NHV_F32) LAUNCH(float);
+    else LAUNCH(__nv_bfloat16);
 #undef LAUNCH
 #undef SCAN
+  }
   NHV_CHECK_LAUNCH("delta_rule");
   return 0;
 }

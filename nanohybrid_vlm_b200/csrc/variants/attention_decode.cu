@@ -286,6 +286,7 @@ struct alignas(64) Params {
   float* part_o;            // [grid][2][16][D]
   float* part_ml;           // [grid][2][16][2]
   int* counters;            // [n_seqs * head_blocks], zero; left zero
+  const float* sinks;       // per query head, or null: exp(sink) joins the softmax denominator once, where a head's sum is final
   int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window;
   float scale_log2;
   FusedQK fq;
@@ -692,6 +693,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
         L += mml[(w * MROWS + R) * 2 + 1] * f;
       }
       if (whole) {
+        if (p.sinks && L > 0.f) L += exp2f(fmaf(p.sinks[kvh * G + g0 + R], LOG2E, -M));
         const float inv = L > 0.f ? 1.0f / L : 0.f;
         bf16* dst = p.out + tok * p.out_stride + (size_t)(kvh * G + g0 + R) * D + c4 * 4;
         *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
@@ -749,6 +751,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
               L += ml[j].y * f;
             }
           }
+          if (p.sinks && L > 0.f) L += exp2f(fmaf(p.sinks[kvh * G + g0 + R], LOG2E, -M));
           const float inv = L > 0.f ? 1.0f / L : 0.f;
           bf16* dst = p.out + tok * p.out_stride + (size_t)(kvh * G + g0 + R) * D + c4 * 4;
           *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
@@ -811,7 +814,7 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
                                       int window, float scale, float* part_o, float* part_ml, int* counters,
                                       const void* q_w, const void* k_w, const float* cos_sin, const int* positions,
                                       const int* slot_mapping, int rotary_dim, int max_position, int store, float eps,
-                                      float weight_offset, cudaStream_t stream) {
+                                      float weight_offset, const float* sinks, cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && page_size % BN == 0 && n_pages > 0 && bt_stride > 0,
               "attention (decode, TMA): pages must be a multiple of %d keys, got %d", BN, page_size);
@@ -888,6 +891,7 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
   p.part_o = part_o;
   p.part_ml = part_ml;
   p.counters = counters;
+  p.sinks = sinks;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv;
   p.page_size = page_size; p.n_pages = n_pages; p.window = window;
   p.scale_log2 = scale * LOG2E;

@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
     const bf16* __restrict__ kv_pages, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int nq, int nkv, int page_size,
-    int n_pages, int window, float scale_log2, int tokens_per_block) {
+    int n_pages, int window, float scale_log2, int tokens_per_block, const float* __restrict__ sinks) {
   constexpr int PF_ROWS = 64 * MTW;                          // rows (token x head of the group) per block
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qbuf = reinterpret_cast<bf16*>(smem_raw);            // [PF_ROWS rows]
@@ -433,6 +433,8 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
       const int R = warp * WROWS + mt * 16 + (lane >> 2) + 8 * i;
       const int tq = R / G, g = R - tq * G;
       if (tq >= tq_n) continue;
+      // a sink per query head: exp(sink) joins the sum once, in the units of the row's running maximum
+      if (sinks && l > 0.f) l += exp2f(fmaf(sinks[kvh * G + g], LOG2E, -st.m[mt][i]));
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       bf16* dst = out + (size_t)(cu_q[seq] + t0 + tq) * out_stride + (size_t)(kvh * G + g) * D + ((lane & 3) << 1);
 #pragma unroll
@@ -517,7 +519,8 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride, const bf16* __restrict__ kv_pages,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int n_seqs, int nq, int nkv,
-    int page_size, int n_pages, int window, float scale_log2, int max_pieces, const FusedQK fq) {
+    int page_size, int n_pages, int window, float scale_log2, int max_pieces, const FusedQK fq,
+    const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
   bf16* vbuf = kbuf + DSTAGES * TILE_ELEMS;
@@ -743,6 +746,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
         L += mml[(w * 16 + R) * 2 + 1] * f;
       }
       if (whole) {
+        if (sinks && L > 0.f) L += exp2f(fmaf(sinks[kvh * G + g0 + R], LOG2E, -M));
         out[tok * out_stride + (size_t)(kvh * G + g0 + R) * D + cc] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
       } else {
         po[R * D + cc] = acc;
@@ -790,6 +794,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
               L += sml[((p0 + j) * gn + R) * 2 + 1] * f;
             }
           }
+          if (sinks && L > 0.f) L += exp2f(fmaf(sinks[kvh * G + g0 + R], LOG2E, -M));
           const float inv = L > 0.f ? 1.0f / L : 0.f;
           bf16* dst = out + tok * out_stride + (size_t)(kvh * G + g0 + R) * D + c4 * 4;
           *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
@@ -836,7 +841,7 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
                             int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                             int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
                             float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                            const FusedQK& fq, cudaStream_t stream) {
+                            const FusedQK& fq, const float* sinks, cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   ATT_REQUIRE(page_size > 0 && n_pages > 0 && bt_stride > 0, "attention: bad page geometry");
   ATT_REQUIRE(q_stride % 8 == 0 && out_stride % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)kv_pages % 16) == 0 &&
@@ -876,12 +881,12 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
       if (wide)
         nhv_launch(attn_prefill_kernel<2>, grid, THREADS, prefill_smem_bytes<2>(), stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-            n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
+            n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block, sinks);
     }
     if (!wide)
       nhv_launch(attn_prefill_kernel<1>, grid, THREADS, prefill_smem_bytes<1>(), stream,
           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-          n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block);
+          n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block, sinks);
   }
   if (n_decode_seqs > 0) {
     ATT_REQUIRE(scratch_o && scratch_ml && counters && max_pieces > 0 && decode_blocks > 0,
@@ -898,7 +903,7 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
     decode_blocks = resident;
     nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces, fq);
+        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces, fq, sinks);
   }
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
@@ -913,11 +918,11 @@ NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int o
                                    int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
                                    int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
                                    float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
-                                   cudaStream_t stream) {
+                                   const float* sinks, cudaStream_t stream) {
   FusedQK none = {};
   return attention_launch(q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs,
                           n_prefill_tokens, n_prefill_seqs, n_decode_seqs, nq, nkv, page_size, n_pages, window, scale,
-                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, stream);
+                          scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, sinks, stream);
 }
 
 // 1 if this head size has the form of the decode kernel that works from the projection's output.
@@ -954,5 +959,5 @@ NHV_API int NHV_FN(nhv_attn_mma_decode_fused_d)(const void* qkv, int qkv_stride,
   fq.weight_offset = weight_offset;
   return attention_launch(qkv, qkv_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs, 0, 0,
                           n_seqs, nq, nkv, page_size, n_pages, window, scale, scratch_o, scratch_ml, counters, max_pieces,
-                          1, fq, stream);
+                          1, fq, nullptr, stream);
 }

@@ -161,6 +161,7 @@ struct alignas(64) Params {
   const int* block_table;
   const int* cu_q;
   const int* kv_len;
+  const float* sinks;     // per query head, or null: exp(sink) joins the softmax denominator (no key, no value, no scale)
   int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, tokens_per_block;
   float scale_log2;
 };
@@ -429,6 +430,8 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     if (ok) ok = mbar_wait(o_full, (uint32_t)(n_tiles - 1) & 1, 11);
     if (ok) {
       tc_fence_after();
+      // the sink: one more term of the sum, in the units of the running reference (an overflow to inf gives inv = 0)
+      if (p.sinks && valid && l > 0.f) l += exp2f(fmaf(p.sinks[kvh * G + g], LOG2E, -m_run));
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       bf16* dst = p.out + (size_t)(q_row0 + t0 + tq) * p.out_stride + (size_t)(kvh * G + g) * D;
 #pragma unroll 1
@@ -508,7 +511,8 @@ NHV_API void* NHV_FN(nhv_attn_tcgen05_error_word_d)() { return nhv_wait_error_ad
 NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
                                        const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                                        int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int nq, int nkv,
-                                       int page_size, int n_pages, int window, float scale, cudaStream_t stream) {
+                                       int page_size, int n_pages, int window, float scale, const float* sinks,
+                                       cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   const int G = nq / nkv;
   ATT_REQUIRE(G <= BM, "attention: a group of %d query heads is beyond the %d rows of a block", G, BM);
@@ -538,6 +542,7 @@ NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, i
   p.block_table = block_table;
   p.cu_q = cu_q;
   p.kv_len = kv_len;
+  p.sinks = sinks;
   p.q_stride = q_stride;
   p.out_stride = out_stride;
   p.bt_stride = bt_stride;

@@ -165,13 +165,15 @@ def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int,
     assert qkv.stride(1) == 1 and qkv.shape[1] == 2 * G * d + H * dv
     assert o.dtype == ba.dtype == a_log.dtype == dt_bias.dtype == state.dtype == torch.float32
     assert o.is_contiguous() and o.shape == (T, H * dv) and ba.is_contiguous() and ba.shape == (T, 2 * H)
-    dev = qkv.device
-    qn = torch.empty(T * G * d * 2, dtype=torch.float32, device=dev)
-    gates = torch.empty(T * H * 2, dtype=torch.float32, device=dev)
+    scratch = torch.empty(T * (2 * G * d + G + H * dv + 2 * H), dtype=torch.float32, device=qkv.device)
+    at, ptrs = 0, []
+    for n in (T * G * d, T * G * d, T * H * dv, T * G, T * H, T * H):     # qn, kn, v32 (16-byte aligned for d, dv in steps of 4), kq, beta, decay
+        ptrs.append(scratch.data_ptr() + 4 * at)
+        at += n
+    qn, kn, v32, kq, beta, decay = ptrs
     call("nhv_delta_rule", dtype_code(qkv), o.data_ptr(), qkv.data_ptr(), qkv.stride(0), ba.data_ptr(), a_log.data_ptr(),
-         dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qn.data_ptr(), qn.data_ptr() + 4 * T * G * d,
-         gates.data_ptr(), gates.data_ptr() + 4 * T * H, batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
-         batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, stream_ptr())
+         dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qn, kn, kq, v32, beta, decay, batch.cu_q.data_ptr(),
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, stream_ptr())
 
 
 def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: int, N: int, G: int) -> None:
@@ -242,7 +244,14 @@ def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int
 def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, dv: int, scale: float, sinks=None,
                    window: int = 0) -> None:
     """Attention of the step's tokens over the cache for layers with a sink and / or value heads of another size
-    than their key heads: picks the kernel for the dtype and sizes."""
+    than their key heads: picks the kernel for the dtype and sizes.  bfloat16 with key and value heads of one size
+    (in steps of 16) runs on the tensor cores like ``attention``; float32 and unequal head sizes on the CUDA cores."""
+    if (q.dtype == torch.bfloat16 and dk == dv and kv_pages.shape[-1] == dk
+            and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
+        attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
+                              batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
+                              nq, nkv, dk, scale, window, sinks)
+        return
     attention_sink_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
                         nq, nkv, dk, dv, scale, sinks, window)
 
@@ -349,7 +358,7 @@ def _tma_decode_scratch(device, head_dim: int, blocks: int):
 def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_kv_len, n_seqs: int, nq: int, nkv: int,
                           head_dim: int, scale: float, window: int, q_weight=None, k_weight=None, cos_sin=None,
                           positions=None, slot_mapping=None, rotary_dim: int = 0, eps: float = 0.0,
-                          weight_offset: float = 0.0, store: bool = False) -> None:
+                          weight_offset: float = 0.0, store: bool = False, sinks=None) -> None:
     launch, blocks = attention_decode.get(head_dim)
     n_pages, two, h, page_size, d = kv_pages.shape
     group = nq // nkv
@@ -362,7 +371,7 @@ def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_
            batch_kv_len.data_ptr(), n_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), part_o.data_ptr(),
            part_ml.data_ptr(), counters.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), _ptr(positions),
            _ptr(slot_mapping), int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0], 1 if store else 0, float(eps),
-           float(weight_offset), stream_ptr())
+           float(weight_offset), _ptr(sinks), stream_ptr())
 
 
 def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float,
@@ -422,12 +431,14 @@ def attention_tcgen05_error(head_dim: int) -> int:
 
 def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_prefill_tokens: int,
                           n_prefill_seqs: int, n_decode_seqs: int, max_kv_len: int, nq: int, nkv: int, head_dim: int,
-                          scale: float, window: int = 0) -> None:
+                          scale: float, window: int = 0, sinks=None) -> None:
     """bfloat16 attention on the tensor cores.  Prompt portions go to the tcgen05 kernel, requests with
     one new token to the kernel that streams the cache with TMA, each where its shape is supported; what
     neither takes runs in the mma.sync kernel, whose single-token path shares a request's tiles between
-    blocks and merges them (scratch: one partial result per piece of a request and head block)."""
-    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len)
+    blocks and merges them (scratch: one partial result per piece of a request and head block).
+    ``sinks`` [nq] float32: exp(sink) joins each head's softmax denominator once (where the head's sum is final)."""
+    _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq and sinks.is_contiguous())
     _contig("kv_pages", kv_pages)
     assert q.dtype == out.dtype == kv_pages.dtype == torch.bfloat16 and q.stride(-1) == 1 and out.stride(-1) == 1
     n_pages, two, h, page_size, d = kv_pages.shape
@@ -440,14 +451,15 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
         attention_tcgen05.get(head_dim)[0](
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
-            nq, nkv, page_size, n_pages, int(window), float(scale), stream_ptr())
+            nq, nkv, page_size, n_pages, int(window), float(scale), _ptr(sinks), stream_ptr())
         if n_decode_seqs == 0:
             return
         n_prefill_tokens = n_prefill_seqs = 0
     if n_decode_seqs > 0 and USE_TMA_DECODE and attention_decode.supports(head_dim, nq, nkv, page_size, n_seqs):
         # single tokens: the kernel that streams the cache with TMA; what is left for the launch below are the
         # prompt portions (if the tcgen05 kernel did not take them)
-        _attention_decode_tma(out, q, None, kv_pages, block_table, cu_q, kv_len, n_seqs, nq, nkv, head_dim, scale, window)
+        _attention_decode_tma(out, q, None, kv_pages, block_table, cu_q, kv_len, n_seqs, nq, nkv, head_dim, scale, window,
+                              sinks=sinks)
         if n_prefill_tokens == 0:
             return
         n_decode_seqs = 0
@@ -467,7 +479,7 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     launch(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
            block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
            n_decode_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), _ptr(scratch_o), _ptr(scratch_ml),
-           _ptr(counters), max_pieces, blocks, stream_ptr())
+           _ptr(counters), max_pieces, blocks, _ptr(sinks), stream_ptr())
 
 
 _sm_counts: dict = {}

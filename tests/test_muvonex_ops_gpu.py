@@ -34,7 +34,9 @@ def step_batch(news, starts, slots):
     """The facts of one packed step that the recurrent kernels read."""
     cu = [0, *np.cumsum(news).tolist()]
     return SimpleNamespace(cu_q=i32(cu), q_start=i32(starts), state_slots=i32(slots), n_seqs=len(news),
-                           n_tokens=int(sum(news)), kv_len=i32([s + n for s, n in zip(starts, news)]))
+                           n_tokens=int(sum(news)), kv_len=i32([s + n for s, n in zip(starts, news)]),
+                           n_prefill_tokens=sum(n for n in news if n > 1), n_prefill_seqs=sum(1 for n in news if n > 1),
+                           n_decode_seqs=sum(1 for n in news if n == 1), max_kv_len=max(s + n for s, n in zip(starts, news)))
 
 
 def portions_of(lengths, cuts):
@@ -261,7 +263,7 @@ def rotary_table(dims, base, scaling, n_pos):
     return torch.cat((ang.cos(), ang.sin()), -1).float()
 
 
-def run_attention(ops, dtype, qkvs, cuts, nq, nkv, dk, dv, page, rot, table, eps, scale, sink, seed=0):
+def run_attention(ops, dtype, qkvs, cuts, nq, nkv, dk, dv, page, rot, table, eps, scale, sink, seed=0, simt=True):
     """Requests' projected rows [L, nq dk + nkv dk + nkv dv] through rotation + norm + cache store and the attention
     kernel, in portions, with shuffled pages in a poisoned pool.  Returns per request [L, nq dv]."""
     rng = np.random.default_rng(seed)
@@ -285,8 +287,12 @@ def run_attention(ops, dtype, qkvs, cuts, nq, nkv, dk, dv, page, rot, table, eps
                             dk, dv, eps)
         out = torch.full((x.shape[0], nq * dv), float("nan"), dtype=dtype, device="cuda")
         b = step_batch(news, starts, [-1] * len(who))
-        ops.attention_sink_simt(out, q, pages, dev(bt), b.cu_q, b.kv_len, len(who), x.shape[0], nq, nkv, dk, dv, scale,
-                                None if sink is None else dev(sink))
+        if simt:
+            ops.attention_sink_simt(out, q, pages, dev(bt), b.cu_q, b.kv_len, len(who), x.shape[0], nq, nkv, dk, dv, scale,
+                                    None if sink is None else dev(sink))
+        else:       # the dispatcher: the tensor-core kernels where the shape allows them
+            ops.attention_sink(out, q, pages, SimpleNamespace(block_tables=dev(bt)), b, nq, nkv, dk, dv, scale,
+                               None if sink is None else dev(sink))
         at = 0
         for r, s, n in zip(who, starts, news):
             got[r][s:s + n] = out[at:at + n].cpu()
@@ -325,6 +331,30 @@ def test_sink_attention_in_portions_against_plain(ops, dtype, nq, nkv, dk, dv, r
     for r, x in enumerate(qkvs):
         want = plain_attention(x, nq, nkv, dk, dv, rot, freqs, 1e-5, 0.3, sinks)
         torch.testing.assert_close(got[r].to(F64), want, **tol(dtype, f32=3e-5, bf16=3e-2))
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,which", [(4, 1, 64, 16, "mma"), (8, 2, 128, 64, "tcgen05"), (6, 2, 64, 128, "tcgen05"),
+                                                  (3, 3, 48, 8, "mma"), (16, 4, 128, 256, "tcgen05"), (8, 2, 128, 64, "mma")])
+def test_sink_attention_on_the_tensor_cores(ops, nq, nkv, d, page, which):
+    """bfloat16 with key and value heads of one size: prompt portions and single tokens of long and short requests
+    in one step through the tensor-core kernels (tcgen05 / TMA where the shape allows, else mma.sync), each with
+    the sink in its head's sum exactly once, also where a request's keys are shared between several blocks."""
+    g = torch.Generator().manual_seed(nq + d)
+    lengths = [900, 130, 301, 40]
+    cuts = [[600, 897, 898, 899], [64, 129], [300], [1, 2, 39]]
+    qkvs = [torch.randn(L, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16) for L in lengths]
+    sinks = torch.randn(nq, generator=g) * 3
+    ops.USE_TCGEN05_ATTENTION = ops.USE_TMA_DECODE = which == "tcgen05"
+    try:
+        got = run_attention(ops, torch.bfloat16, qkvs, cuts, nq, nkv, d, d, page, 0, None, 1e-6, 0.25, sinks, simt=False)
+    finally:
+        ops.USE_TCGEN05_ATTENTION = ops.USE_TMA_DECODE = True
+    assert ops.take_wait_errors() == [], "a bounded wait of a kernel ran out"
+    for r, x in enumerate(qkvs):
+        want = plain_attention(x, nq, nkv, d, d, 0, None, 1e-6, 0.25, sinks)
+        torch.testing.assert_close(got[r].to(F64), want, rtol=3e-2, atol=3e-2)
+    # without the sink the same rows differ: the test would see a sink that was left out
+    assert not torch.allclose(plain_attention(qkvs[3], nq, nkv, d, d, 0, None, 1e-6, 0.25, None), got[3].to(F64), atol=3e-2)
 
 
 @pytest.mark.parametrize("page", [7, 16, 64])
