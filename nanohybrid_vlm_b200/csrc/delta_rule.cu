@@ -95,11 +95,12 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// R: rows of a column per lane (a multiple of 4, R * 8 >= d).  qn, kn [T, G, d]; v32 [T, H, dv]; kq [T, G]; all fp32.
+// R: rows of a column per lane (a multiple of 4, R * 8 >= d).  qn, kn [T, G, d]; kq [T, G]; v32: rows of v_stride
+// floats whose first H * dv are the token's values; all fp32.
 template <int R>
 __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     float* __restrict__ o_out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ kq,
-    const float* __restrict__ v32, const float* __restrict__ beta, const float* __restrict__ decay,
+    const float* __restrict__ v32, int v_stride, const float* __restrict__ beta, const float* __restrict__ decay,
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
     const int* __restrict__ slots, int G, int H, int d, int dv) {
   extern __shared__ __align__(16) float smem[];
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     }
     for (int i = tid; i < cn * c4; i += DF_THREADS) {
       const int tt = i / c4, c = i - tt * c4;
-      cp_async16(vs + tt * DF_COLS + 4 * c, v32 + ((size_t)(first + c0 + tt) * H + h) * dv + col0 + 4 * c);
+      cp_async16(vs + tt * DF_COLS + 4 * c, v32 + (size_t)(first + c0 + tt) * v_stride + h * dv + col0 + 4 * c);
     }
     for (int i = tid; i < cn * 3; i += DF_THREADS) {
       const int tt = i / 3, w = i - tt * 3;
@@ -322,11 +323,15 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
   NHV_REQUIRE(d > 0 && d <= 256 && dv > 0, "delta_rule: a q/k head of %d is beyond the supported 256", d);
   NHV_REQUIRE(state_stride >= (long)H * d * dv, "delta_rule: the state holds fewer than heads * d * dv floats");
   const bool fast = d % 4 == 0 && dv % 4 == 0;
+  // values that are fp32 already are read where they lie (16-byte pieces: the rows' stride and start in steps of 4)
+  const bool v_in_place = fast && dtype == NHV_F32 && qkv_stride % 4 == 0 && ((uintptr_t)qkv % 16) == 0;
+  const float* v_src = v_in_place ? (const float*)qkv + 2 * G * d : v32;
+  const int v_stride = v_in_place ? qkv_stride : H * dv;
   const long work = (long)n_tokens * (H * dv > 32 * G ? H * dv : 32 * G);
   const int prep_blocks = (int)(work / 256 + 1 < 148 * 8 ? work / 256 + 1 : 148 * 8);
   const int v_off = 2 * G * d;
 #define PREP(T)                                                                                                      \
-  nhv_launch(delta_prepare_kernel<T>, prep_blocks, 256, 0, stream, qn, kn, kq, fast ? v32 : (float*)nullptr, beta,   \
+  nhv_launch(delta_prepare_kernel<T>, prep_blocks, 256, 0, stream, qn, kn, kq, fast && !v_in_place ? v32 : (float*)nullptr, beta, \
              decay, (const T*)qkv, qkv_stride, ba, a_log, dt_bias, n_tokens, G, H, d, dv)
   if (dtype == NHV_F32) PREP(float);
   else if (dtype == NHV_BF16) PREP(__nv_bfloat16);
@@ -344,7 +349,7 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
       attr = true;                                                                                                   \
     }                                                                                                                \
     nhv_launch(delta_scan_fast_kernel<R>, grid, DF_THREADS, smem, stream, o_out, (const float*)qn, (const float*)kn, \
-               (const float*)kq, (const float*)v32, (const float*)beta, (const float*)decay, state, state_stride,   \
+               (const float*)kq, v_src, v_stride, (const float*)beta, (const float*)decay, state, state_stride,     \
                cu_q, q_start, slots, G, H, d, dv);                                                                   \
   } while (0)
     if (d <= 32) FAST(4);

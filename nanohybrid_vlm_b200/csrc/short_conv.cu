@@ -12,8 +12,8 @@
 constexpr int SC_MAX_TAPS = 8;
 constexpr int SC_TOKENS = 8;        // tokens per block of the output kernel
 
-template <typename T>
-__global__ void short_conv_silu_kernel(T* __restrict__ y, int y_stride, const T* __restrict__ x, int x_stride,
+template <typename T, typename TO>
+__global__ void short_conv_silu_kernel(TO* __restrict__ y, int y_stride, const T* __restrict__ x, int x_stride,
                                        const T* __restrict__ w, const T* __restrict__ bias,
                                        const float* __restrict__ state, long state_stride,
                                        const int* __restrict__ cu_q, const int* __restrict__ q_start,
@@ -50,7 +50,7 @@ __global__ void short_conv_silu_kernel(T* __restrict__ y, int y_stride, const T*
         acc = fmaf(wk[j], v, acc);
       }
     }
-    y[(size_t)t * y_stride + c] = from_f32<T>(acc / (1.0f + expf(-acc)));
+    y[(size_t)t * y_stride + c] = from_f32<TO>(acc / (1.0f + expf(-acc)));
   }
 }
 
@@ -81,21 +81,26 @@ __global__ void short_conv_state_kernel(const T* __restrict__ x, int x_stride, f
     if (j < K - 1) st[(size_t)j * C + c] = keep[j];
 }
 
-NHV_API int nhv_short_conv_silu(int dtype, void* y, int y_stride, const void* x, int x_stride, const void* w,
+// dtype: of x, the filters and the bias; out_dtype: of y (fp32 where a recurrence reads it next)
+NHV_API int nhv_short_conv_silu(int dtype, int out_dtype, void* y, int y_stride, const void* x, int x_stride, const void* w,
                                 const void* bias, float* state, long state_stride, const int* cu_q,
                                 const int* q_start, const int* slots, int n_seqs, int n_tokens, int C, int K,
                                 cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
+  NHV_REQUIRE(out_dtype == dtype || out_dtype == NHV_F32, "short_conv: the output is of the input's type or fp32");
   NHV_REQUIRE(C > 0 && K >= 1 && K <= SC_MAX_TAPS, "short_conv: %d taps are beyond the supported %d", K, SC_MAX_TAPS);
   NHV_REQUIRE(K == 1 || (state && state_stride >= (long)(K - 1) * C), "short_conv: the state holds fewer than (taps - 1) * channels floats");
   const int threads = 128;
   dim3 grid((n_tokens + SC_TOKENS - 1) / SC_TOKENS, (C + threads - 1) / threads);
   dim3 grid2(n_seqs, (C + threads - 1) / threads);
+#define OUT(T, TO)                                                                                                 \
+  nhv_launch(short_conv_silu_kernel<T, TO>, grid, threads, 0, stream, (TO*)y, y_stride, (const T*)x, x_stride,     \
+             (const T*)w, (const T*)bias, (const float*)state, state_stride, cu_q, q_start, slots, n_seqs,         \
+             n_tokens, C, K)
 #define LAUNCH(T)                                                                                                  \
   do {                                                                                                             \
-    nhv_launch(short_conv_silu_kernel<T>, grid, threads, 0, stream, (T*)y, y_stride, (const T*)x, x_stride,        \
-               (const T*)w, (const T*)bias, (const float*)state, state_stride, cu_q, q_start, slots, n_seqs,       \
-               n_tokens, C, K);                                                                                    \
+    if (out_dtype == NHV_F32) OUT(T, float);                                                                       \
+    else OUT(T, T);                                                                                                \
     if (K > 1)                                                                                                     \
       nhv_launch(short_conv_state_kernel<T>, grid2, threads, 0, stream, (const T*)x, x_stride, state, state_stride, \
                  cu_q, q_start, slots, C, K);                                                                      \
@@ -104,6 +109,7 @@ NHV_API int nhv_short_conv_silu(int dtype, void* y, int y_stride, const void* x,
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
   else NHV_REQUIRE(false, "short_conv: unknown dtype %d", dtype);
 #undef LAUNCH
+#undef OUT
   NHV_CHECK_LAUNCH("short_conv");
   return 0;
 }

@@ -4,9 +4,13 @@
 // Per head, with the state S [N, P] (fp32, carried per request), group gr of the head:
 //   dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B_t x_t^T;  y_t = S^T C_t + D x_t
 //
-// ssd_scan: one block per (request, head, tile of 64 columns of S).  Thread (column j, part p of 4) keeps rows
-// p, p + 4, ... of column j in registers; the sum over rows ends with two shuffles.  Tokens go through shared memory
-// in chunks of 16.  The state of a slot is stored transposed, [head][P][N].  A request with q_start == 0 starts from
+// ssd_scan_fast (fp32 inputs, sizes in steps of 4): the columns of S are independent of one another (column j:
+// S_j <- a S_j + dt x_j B, y_j = S_j . C + D x_j), so a block takes (request, head, 16 columns) and a column lives
+// in the registers of 8 lanes, each with N / 8 rows in groups of 4 (one 16-byte read of B and of C from shared
+// memory serves 4 rows); the sum over rows ends with three shuffles.  Tokens reach shared memory by cp.async, 16 at
+// a time, the next 16 while these are worked on; dt and the decay of the next 16 are computed meanwhile.
+// ssd_scan (any size and type): 64 columns a block, 4 lanes a column, plain loads.
+// The state of a slot is stored transposed, [head][P][N].  A request with q_start == 0 starts from
 // zeros; one without a slot (slot < 0) is skipped and its outputs are cleared.
 //
 // gated_rmsnorm: rows of fp32 values y [T, n_groups * size], a gate z in the storage type, a weight w:
@@ -106,6 +110,133 @@ __global__ void __launch_bounds__(SS_COLS * SS_PARTS) ssd_scan_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------- the scan for fp32 inputs and sizes in steps of 4
+constexpr int SF_COLS = 16;
+constexpr int SF_LANES = 8;
+constexpr int SF_CHUNK = 16;
+constexpr int SF_THREADS = SF_COLS * SF_LANES;
+
+__device__ __forceinline__ void ss_cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void ss_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N_> __device__ __forceinline__ void ss_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N_)); }
+
+template <int R>
+__global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
+    float* __restrict__ y, const float* __restrict__ xbc, int xbc_stride, const float* __restrict__ dt_raw, int dt_stride,
+    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+    float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int H, int P, int N, int G) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_prologue();
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SF_COLS;
+  const int gr = h / (H / G);
+  const int inner = H * P;
+  const int first = cu_q[s], n = cu_q[s + 1] - first;
+  const int slot = slots[s];
+  const int tid = threadIdx.x;
+  const int ncol = min(SF_COLS, P - col0);             // a multiple of 4
+  if (slot < 0) {
+    for (int i = tid; i < n * ncol; i += SF_THREADS) y[(size_t)(first + i / ncol) * inner + h * P + col0 + i % ncol] = 0.f;
+    return;
+  }
+  const int stage_floats = SF_CHUNK * (2 * N + SF_COLS + 2);
+  const int cl = tid / SF_LANES, part = tid % SF_LANES;
+  const bool live = cl < ncol;
+  const int col = col0 + (live ? cl : 0);
+  float* st = state + (size_t)slot * state_stride + ((size_t)h * P + col) * N;
+  const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+  float S[R];
+  const bool fresh = q_start[s] == 0;
+#pragma unroll
+  for (int j = 0; j < R / 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 4 * (part + SF_LANES * j) + e;
+      S[4 * j + e] = (live && !fresh && i < N) ? st[i] : 0.f;
+    }
+
+  auto fetch = [&](int c0, int stage) {
+    float* Bs = smem + stage * stage_floats;           // [CHUNK][N]
+    float* Cs = Bs + SF_CHUNK * N;                     // [CHUNK][N]
+    float* xs = Cs + SF_CHUNK * N;                     // [CHUNK][SF_COLS]
+    const int cn = min(SF_CHUNK, n - c0);
+    const int n4 = N >> 2, c4 = ncol >> 2;
+    for (int i = tid; i < cn * n4; i += SF_THREADS) {
+      const int tt = i / n4, c = i - tt * n4;
+      const float* row = xbc + (size_t)(first + c0 + tt) * xbc_stride + inner + gr * N + 4 * c;
+      ss_cp_async16(Bs + tt * N + 4 * c, row);
+      ss_cp_async16(Cs + tt * N + 4 * c, row + (size_t)G * N);
+    }
+    for (int i = tid; i < cn * c4; i += SF_THREADS) {
+      const int tt = i / c4, c = i - tt * c4;
+      ss_cp_async16(xs + tt * SF_COLS + 4 * c, xbc + (size_t)(first + c0 + tt) * xbc_stride + h * P + col0 + 4 * c);
+    }
+  };
+
+  const int n_chunks = (n + SF_CHUNK - 1) / SF_CHUNK;
+  float dt_next = 0.f;                                 // thread tt < CHUNK: the raw dt of token tt of the chunk to come
+  if (n_chunks > 0) {
+    fetch(0, 0);
+    if (tid < min(SF_CHUNK, n)) dt_next = dt_raw[(size_t)(first + tid) * dt_stride + h];
+  }
+  ss_cp_async_commit();
+  for (int ci = 0; ci < n_chunks; ++ci) {
+    const int c0 = ci * SF_CHUNK, stage = ci & 1;
+    const int cn = min(SF_CHUNK, n - c0);
+    if (ci + 1 < n_chunks) fetch(c0 + SF_CHUNK, stage ^ 1);
+    ss_cp_async_commit();
+    float* ds = smem + stage * stage_floats + SF_CHUNK * (2 * N + SF_COLS);     // [CHUNK][2]: decay, dt
+    if (tid < cn) {
+      const float dt = ss_softplus(dt_next + bias);
+      ds[2 * tid] = expf(-rate * dt);
+      ds[2 * tid + 1] = dt;
+    }
+    ss_cp_async_wait<1>();
+    __syncthreads();
+    if (ci + 1 < n_chunks && tid < min(SF_CHUNK, n - c0 - SF_CHUNK))
+      dt_next = dt_raw[(size_t)(first + c0 + SF_CHUNK + tid) * dt_stride + h];
+    const float* Bs = smem + stage * stage_floats;
+    const float* Cs = Bs + SF_CHUNK * N;
+    const float* xs = Cs + SF_CHUNK * N;
+    for (int tt = 0; tt < cn; ++tt) {
+      const float a = ds[2 * tt], dt = ds[2 * tt + 1];
+      const float xv = live ? xs[tt * SF_COLS + cl] : 0.f;
+      const float dx = dt * xv;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const int c = part + SF_LANES * j;
+        if (4 * c < N) {
+          const float4 bb = *reinterpret_cast<const float4*>(Bs + tt * N + 4 * c);
+          const float4 cc = *reinterpret_cast<const float4*>(Cs + tt * N + 4 * c);
+          S[4 * j] = fmaf(a, S[4 * j], dx * bb.x);         acc[0] = fmaf(S[4 * j], cc.x, acc[0]);
+          S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * bb.y); acc[1] = fmaf(S[4 * j + 1], cc.y, acc[1]);
+          S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * bb.z); acc[2] = fmaf(S[4 * j + 2], cc.z, acc[2]);
+          S[4 * j + 3] = fmaf(a, S[4 * j + 3], dx * bb.w); acc[3] = fmaf(S[4 * j + 3], cc.w, acc[3]);
+        }
+      }
+      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+      for (int off = 1; off < SF_LANES; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      if (live && part == 0) y[(size_t)(first + c0 + tt) * inner + h * P + col] = fmaf(skip, xv, sum);
+    }
+    __syncthreads();                                   // the stage is free for the fetch after next
+  }
+  ss_cp_async_wait<0>();
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < R / 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 4 * (part + SF_LANES * j) + e;
+        if (i < N) st[i] = S[4 * j + e];
+      }
+  }
+}
+
 // xbc [T, H*P + 2*G*N] (x, then B, then C), dt_raw [T, >= H] fp32, y [T, H*P] fp32
 NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, const float* dt_raw, int dt_stride,
                          const float* dt_bias, const float* a_log, const float* d_skip, float* state,
@@ -115,6 +246,28 @@ NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, c
   NHV_REQUIRE(G > 0 && H > 0 && H % G == 0, "ssd_scan: %d heads do not divide into %d groups", H, G);
   NHV_REQUIRE(N > 0 && N <= 256 && P > 0, "ssd_scan: a state of %d rows is beyond the supported 256", N);
   NHV_REQUIRE(state_stride >= (long)H * P * N, "ssd_scan: the state holds fewer than heads * P * N floats");
+  if (dtype == NHV_F32 && N % 4 == 0 && P % 4 == 0 && xbc_stride % 4 == 0 && ((uintptr_t)xbc % 16) == 0) {
+    const size_t fsmem = (size_t)2 * SF_CHUNK * (2 * N + SF_COLS + 2) * sizeof(float);
+    dim3 fgrid(n_seqs, H, (P + SF_COLS - 1) / SF_COLS);
+#define FAST(R)                                                                                                      \
+  do {                                                                                                               \
+    static bool attr = false;                                                                                        \
+    if (!attr) {                                                                                                     \
+      NHV_CUDA(cudaFuncSetAttribute(ssd_scan_fast_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                    (int)((size_t)2 * SF_CHUNK * (2 * 256 + SF_COLS + 2) * sizeof(float))), "ssd_scan"); \
+      attr = true;                                                                                                   \
+    }                                                                                                                \
+    nhv_launch(ssd_scan_fast_kernel<R>, fgrid, SF_THREADS, fsmem, stream, y, (const float*)xbc, xbc_stride, dt_raw,  \
+               dt_stride, dt_bias, a_log, d_skip, state, state_stride, cu_q, q_start, slots, H, P, N, G);            \
+  } while (0)
+    if (N <= 32) FAST(4);
+    else if (N <= 64) FAST(8);
+    else if (N <= 128) FAST(16);
+    else FAST(32);
+#undef FAST
+    NHV_CHECK_LAUNCH("ssd_scan");
+    return 0;
+  }
   const int rows = (N + SS_PARTS - 1) / SS_PARTS;
   const size_t smem = ((size_t)SS_CHUNK * (2 * N + SS_COLS) + 2 * SS_CHUNK) * sizeof(float);
   dim3 grid(n_seqs, H, (P + SS_COLS - 1) / SS_COLS);

@@ -145,13 +145,15 @@ def scaled_sum(out, a, b, ca: float, cb: float) -> None:
 
 def short_conv_silu(out, x, weight, bias, state, batch) -> None:
     """out [T, C] = silu(causal convolution over time of x [T, C] (a view with unit column stride) with weight [C, K]
-    (+ bias)); ``state`` [slots, (K - 1) * C] float32 holds each request's last K - 1 inputs and is moved on."""
+    (+ bias)); ``state`` [slots, (K - 1) * C] float32 holds each request's last K - 1 inputs and is moved on.  ``out`` is
+    of x's type, or float32 (for a recurrence that reads it next)."""
     _need_cuda(out, x, weight, bias, state)
     C, K = weight.shape
     assert x.dim() == 2 and x.shape[1] == C and x.stride(1) == 1 and out.shape == x.shape and out.stride(1) == 1
-    assert out.dtype == x.dtype == weight.dtype and weight.is_contiguous() and state.dtype == torch.float32
+    assert x.dtype == weight.dtype and out.dtype in (x.dtype, torch.float32) and weight.is_contiguous()
+    assert state.dtype == torch.float32
     assert state.dim() == 2 and state.stride(1) == 1 and (bias is None or (bias.dtype == x.dtype and bias.numel() == C))
-    call("nhv_short_conv_silu", dtype_code(x), out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), weight.data_ptr(),
+    call("nhv_short_conv_silu", dtype_code(x), dtype_code(out), out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), weight.data_ptr(),
          _ptr(bias), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
          batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
 

@@ -68,7 +68,7 @@ class GatedDeltaRule(Mixer):
         ops.linear(proj, x, self.w_qkvg)
         ba = self.new(T, 2 * self.H, dtype=torch.float32)
         ops.linear_f32(ba, x, self.w_ba)
-        qkv = self.new(T, C)
+        qkv = self.new(T, C, dtype=torch.float32)      # what enters the recurrence stays 32-bit
         ops.short_conv_silu(qkv, proj[:, :C], self.w_conv, None, conv_state, batch)
         o = self.new(T, self.v_size, dtype=torch.float32)
         ops.delta_rule(o, qkv, ba, self.w_A_log, self.w_dt_bias, rule_state, batch, self.G, self.H, self.d, self.dv)

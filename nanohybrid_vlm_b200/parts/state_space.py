@@ -72,7 +72,7 @@ class Mamba2(Mixer):
         ops.linear(zxbc, x, self.w_in_main)
         dt = self.new(T, self.heads, dtype=torch.float32)
         ops.linear_f32(dt, x, self.w_in_dt)
-        xbc = self.new(T, self.conv_channels)
+        xbc = self.new(T, self.conv_channels, dtype=torch.float32)      # what enters the recurrence stays 32-bit
         ops.short_conv_silu(xbc, zxbc[:, self.inner:], self.w_conv, self.w_conv_b, conv_state, batch)
         y = self.new(T, self.inner, dtype=torch.float32)
         ops.ssd_scan(y, xbc, dt, self.w_dt_bias, self.w_A_log, self.w_D, ssm_state, batch, self.heads, self.P, self.N,

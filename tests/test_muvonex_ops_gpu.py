@@ -80,11 +80,12 @@ def test_short_conv_over_portions_and_reused_slots(ops, dtype, C, K, bias):
     for r in range(3):
         torch.testing.assert_close(got[r].to(F64), want[r], **tol(dtype))
     # slot 2 held request 0's last inputs: a new request there must not see them
+    # (its output in float32, as the recurrent mixers ask for it: nothing is rounded to the inputs' type)
     x = torch.randn(3, C, generator=g).to(dtype)
-    out = torch.empty(3, C, dtype=dtype, device="cuda")
+    out = torch.empty(3, C, dtype=torch.float32, device="cuda")
     ops.short_conv_silu(out, dev(x), dev(w), None if b is None else dev(b), state, step_batch([3], [0], [2]))
     torch.testing.assert_close(out.cpu().to(F64), pm.silu(pm.short_conv(x.to(F64), w.to(F64), None if b is None else b.to(F64))),
-                               **tol(dtype))
+                               **tol(torch.float32))
 
 
 # ---------------------------------------------------------------- gated delta rule
@@ -108,7 +109,8 @@ def plain_delta(qkv, ba, a_log, dt_bias, G, H, d, dv):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("G,H,d,dv", [(2, 4, 24, 40), (3, 3, 48, 16), (1, 5, 100, 72), (2, 2, 16, 130), (1, 1, 256, 8)])
+@pytest.mark.parametrize("G,H,d,dv", [(2, 4, 24, 40), (3, 3, 48, 16), (1, 5, 100, 72), (2, 2, 16, 130), (1, 1, 256, 8),
+                                      (2, 2, 30, 18), (1, 2, 128, 128), (1, 3, 7, 5)])
 def test_delta_rule_over_portions_and_reused_slots(ops, dtype, G, H, d, dv):
     g = torch.Generator().manual_seed(G * 1000 + d)
     lengths, cuts, slots = [41, 19, 6], [[2, 3, 20, 37], [18], [1, 2, 3, 4, 5]], [1, 3, 0]
@@ -184,7 +186,8 @@ def plain_ssd(xbc, dt_raw, dt_bias, a_log, skip, H, P, N, G):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,P,N,G", [(4, 24, 16, 2), (6, 40, 48, 3), (3, 130, 20, 1), (2, 8, 256, 2), (5, 64, 7, 5)])
+@pytest.mark.parametrize("H,P,N,G", [(4, 24, 16, 2), (6, 40, 48, 3), (3, 130, 20, 1), (2, 8, 256, 2), (5, 64, 7, 5),
+                                     (2, 64, 128, 1), (3, 20, 100, 3)])
 def test_ssd_scan_over_portions_and_reused_slots(ops, dtype, H, P, N, G):
     g = torch.Generator().manual_seed(H * 100 + N)
     lengths, cuts, slots = [37, 12, 5], [[2, 3, 19, 36], [11], [1, 2, 3, 4]], [3, 0, 2]
