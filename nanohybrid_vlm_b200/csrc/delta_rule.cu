@@ -104,7 +104,9 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
     const int* __restrict__ slots, int G, int H, int d, int dv) {
   extern __shared__ __align__(16) float smem[];
-  pdl_prologue();
+  // a long kernel of few blocks: the kernel behind it is let in only at the end, so that its blocks do not sit on
+  // the SMs beside these for the whole scan
+  pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DF_COLS;
   const int g = h / (H / G);
   const int first = cu_q[s], n = cu_q[s + 1] - first;
@@ -116,33 +118,43 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
       o_out[((size_t)(first + i / ncol) * H + h) * dv + col0 + i % ncol] = 0.f;
     return;
   }
-  const int stage_floats = DF_CHUNK * (2 * d + DF_COLS + 4);
+  constexpr int DP = R * DF_LANES;                      // a row of q or k in shared memory: d floats, then zeros
+  constexpr int stage_floats = DF_CHUNK * (2 * DP + DF_COLS + 4);
+  if (d < DP)                                          // (cp.async never writes the padding)
+    for (int i = tid; i < 2 * 2 * DF_CHUNK * (DP - d); i += DF_THREADS) {
+      const int row = i / (DP - d), c = i - row * (DP - d);          // row: stage, q or k, token
+      smem[(row / (2 * DF_CHUNK)) * stage_floats + (row % (2 * DF_CHUNK)) * DP + d + c] = 0.f;
+    }
   const int cl = tid / DF_LANES, part = tid % DF_LANES;
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
   float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + col) * d;
   float S[R];
   const bool fresh = q_start[s] == 0;
+  const bool st_vec = ((uintptr_t)st % 16) == 0;       // d is a multiple of 4: then every group of 4 rows is 16-byte aligned
 #pragma unroll
-  for (int j = 0; j < R / 4; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = 4 * (part + DF_LANES * j) + e;
-      S[4 * j + e] = (live && !fresh && i < d) ? st[i] : 0.f;
+  for (int j = 0; j < R / 4; ++j) {
+    const int i = 4 * (part + DF_LANES * j);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && !fresh && i < d) {
+      if (st_vec) v = *reinterpret_cast<const float4*>(st + i);
+      else v = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
     }
+    S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+  }
 
   auto fetch = [&](int c0, int stage) {
-    float* qs = smem + stage * stage_floats;           // [CHUNK][d]
-    float* ks = qs + DF_CHUNK * d;                     // [CHUNK][d]
-    float* vs = ks + DF_CHUNK * d;                     // [CHUNK][DF_COLS]
+    float* qs = smem + stage * stage_floats;           // [CHUNK][DP]
+    float* ks = qs + DF_CHUNK * DP;                    // [CHUNK][DP]
+    float* vs = ks + DF_CHUNK * DP;                    // [CHUNK][DF_COLS]
     float* sc = vs + DF_CHUNK * DF_COLS;               // [CHUNK][4]: decay, beta, k . q
     const int cn = min(DF_CHUNK, n - c0);
     const int d4 = d >> 2, c4 = ncol >> 2;
     for (int i = tid; i < cn * d4; i += DF_THREADS) {
       const int tt = i / d4, c = i - tt * d4;
       const size_t row = ((size_t)(first + c0 + tt) * G + g) * d + 4 * c;
-      cp_async16(qs + tt * d + 4 * c, qn + row);
-      cp_async16(ks + tt * d + 4 * c, kn + row);
+      cp_async16(qs + tt * DP + 4 * c, qn + row);
+      cp_async16(ks + tt * DP + 4 * c, kn + row);
     }
     for (int i = tid; i < cn * c4; i += DF_THREADS) {
       const int tt = i / c4, c = i - tt * c4;
@@ -164,23 +176,19 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const float* qs = smem + stage * stage_floats;
-    const float* ks = qs + DF_CHUNK * d;
-    const float* vs = ks + DF_CHUNK * d;
+    const float* qs = smem + stage * stage_floats + 4 * part;
+    const float* ks = qs + DF_CHUNK * DP;
+    const float* vs = smem + stage * stage_floats + 2 * DF_CHUNK * DP;
     const float* sc = vs + DF_CHUNK * DF_COLS;
     const int cn = min(DF_CHUNK, n - c0);
+#pragma unroll 2
     for (int tt = 0; tt < cn; ++tt) {
       const float gt = sc[tt * 4], bt = sc[tt * 4 + 1], kqt = sc[tt * 4 + 2];
       float4 kk[R / 4], qq[R / 4];
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        const int c = part + DF_LANES * j;
-        if (4 * c < d) {
-          kk[j] = *reinterpret_cast<const float4*>(ks + tt * d + 4 * c);
-          qq[j] = *reinterpret_cast<const float4*>(qs + tt * d + 4 * c);
-        } else {
-          kk[j] = qq[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        kk[j] = *reinterpret_cast<const float4*>(ks + tt * DP + 4 * DF_LANES * j);
+        qq[j] = *reinterpret_cast<const float4*>(qs + tt * DP + 4 * DF_LANES * j);
       }
       float ak[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -209,14 +217,19 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     __syncthreads();                                   // the stage is free for the fetch after next
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();
   if (live) {
 #pragma unroll
-    for (int j = 0; j < R / 4; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = 4 * (part + DF_LANES * j) + e;
-        if (i < d) st[i] = S[4 * j + e];
+    for (int j = 0; j < R / 4; ++j) {
+      const int i = 4 * (part + DF_LANES * j);
+      if (i < d) {
+        if (st_vec) {
+          *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        } else {
+          st[i] = S[4 * j]; st[i + 1] = S[4 * j + 1]; st[i + 2] = S[4 * j + 2]; st[i + 3] = S[4 * j + 3];
+        }
       }
+    }
   }
 }
 
@@ -338,17 +351,18 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
   else NHV_REQUIRE(false, "delta_rule: unknown dtype %d", dtype);
 #undef PREP
   if (fast) {
-    const size_t smem = (size_t)2 * DF_CHUNK * (2 * d + DF_COLS + 4) * sizeof(float);
     dim3 grid(n_seqs, H, (dv + DF_COLS - 1) / DF_COLS);
 #define FAST(R)                                                                                                      \
   do {                                                                                                               \
     static bool attr = false;                                                                                        \
     if (!attr) {                                                                                                     \
       NHV_CUDA(cudaFuncSetAttribute(delta_scan_fast_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
-                                    (int)((size_t)2 * DF_CHUNK * (2 * 256 + DF_COLS + 4) * sizeof(float))), "delta_rule"); \
+                                    232448), "delta_rule");                                                  \
       attr = true;                                                                                                   \
     }                                                                                                                \
-    nhv_launch(delta_scan_fast_kernel<R>, grid, DF_THREADS, smem, stream, o_out, (const float*)qn, (const float*)kn, \
+    nhv_launch(delta_scan_fast_kernel<R>, grid, DF_THREADS,                                                          \
+               nhv_spread_smem((size_t)2 * DF_CHUNK * (2 * R * DF_LANES + DF_COLS + 4) * sizeof(float),             \
+                               (long)grid.x * grid.y * grid.z), stream, o_out, (const float*)qn, (const float*)kn, \
                (const float*)kq, v_src, v_stride, (const float*)beta, (const float*)decay, state, state_stride,     \
                cu_q, q_start, slots, G, H, d, dv);                                                                   \
   } while (0)

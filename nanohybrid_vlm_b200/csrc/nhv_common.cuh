@@ -85,6 +85,20 @@ inline cudaError_t nhv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Shared memory to ask for so that a kernel of few, long-running blocks gets its blocks spread over the SMs: the
+// block scheduler fills an SM as far as resources allow, and behind another kernel's tail that can leave several
+// such blocks on one SM and other SMs idle.  `need`: what the block uses; `blocks`: the grid.  With a grid of up to
+// `sms` blocks each block takes an SM's whole shared memory, with up to 2 * sms half of it, and so on; large grids
+// ask for what they need.
+inline size_t nhv_spread_smem(size_t need, long blocks, int sms = 148) {
+  const long per_sm = (blocks + sms - 1) / sms;
+  if (per_sm > 6) return need;
+  const size_t share = (size_t)(233472 / per_sm) - 1024;      // 228 KB an SM, 1 KB reserved per block
+  const size_t most = 232448;                                  // 227 KB a block
+  const size_t want = share < most ? share : most;
+  return want > need ? want : need;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -10,17 +10,20 @@
 #include "nhv_common.cuh"
 
 constexpr int SC_MAX_TAPS = 8;
-constexpr int SC_TOKENS = 8;        // tokens per block of the output kernel
+constexpr int SC_TOKENS = 8;        // tokens per block of the output kernel in a long step (the filters are read once for them);
+                                    // a short step takes one token per block: finding a token's request is a chain of
+                                    // dependent loads that the tokens of a block would go through one after another
 
 template <typename T, typename TO>
 __global__ void short_conv_silu_kernel(TO* __restrict__ y, int y_stride, const T* __restrict__ x, int x_stride,
                                        const T* __restrict__ w, const T* __restrict__ bias,
                                        const float* __restrict__ state, long state_stride,
                                        const int* __restrict__ cu_q, const int* __restrict__ q_start,
-                                       const int* __restrict__ slots, int n_seqs, int n_tokens, int C, int K) {
+                                       const int* __restrict__ slots, int n_seqs, int n_tokens, int C, int K,
+                                       int tokens_per_block) {
   pdl_prologue();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  const int t0 = blockIdx.x * SC_TOKENS;
+  const int t0 = blockIdx.x * tokens_per_block;
   if (c >= C || t0 >= n_tokens) return;
   float wk[SC_MAX_TAPS];
 #pragma unroll
@@ -33,7 +36,7 @@ __global__ void short_conv_silu_kernel(TO* __restrict__ y, int y_stride, const T
     if (cu_q[mid] <= t0) lo = mid; else hi = mid - 1;
   }
   int s = lo;
-  const int t_end = min(t0 + SC_TOKENS, n_tokens);
+  const int t_end = min(t0 + tokens_per_block, n_tokens);
   for (int t = t0; t < t_end; ++t) {
     while (s + 1 < n_seqs && cu_q[s + 1] <= t) ++s;
     const int i = t - cu_q[s];                      // index within this step's portion
@@ -91,12 +94,13 @@ NHV_API int nhv_short_conv_silu(int dtype, int out_dtype, void* y, int y_stride,
   NHV_REQUIRE(C > 0 && K >= 1 && K <= SC_MAX_TAPS, "short_conv: %d taps are beyond the supported %d", K, SC_MAX_TAPS);
   NHV_REQUIRE(K == 1 || (state && state_stride >= (long)(K - 1) * C), "short_conv: the state holds fewer than (taps - 1) * channels floats");
   const int threads = 128;
-  dim3 grid((n_tokens + SC_TOKENS - 1) / SC_TOKENS, (C + threads - 1) / threads);
+  const int tokens_per_block = n_tokens <= 512 ? 1 : SC_TOKENS;
+  dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, (C + threads - 1) / threads);
   dim3 grid2(n_seqs, (C + threads - 1) / threads);
 #define OUT(T, TO)                                                                                                 \
   nhv_launch(short_conv_silu_kernel<T, TO>, grid, threads, 0, stream, (TO*)y, y_stride, (const T*)x, x_stride,     \
              (const T*)w, (const T*)bias, (const float*)state, state_stride, cu_q, q_start, slots, n_seqs,         \
-             n_tokens, C, K)
+             n_tokens, C, K, tokens_per_block)
 #define LAUNCH(T)                                                                                                  \
   do {                                                                                                             \
     if (out_dtype == NHV_F32) OUT(T, float);                                                                       \

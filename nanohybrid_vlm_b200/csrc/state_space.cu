@@ -130,7 +130,9 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
     const int* __restrict__ slots, int H, int P, int N, int G) {
   extern __shared__ __align__(16) float smem[];
-  pdl_prologue();
+  // a long kernel of few blocks: the kernel behind it is let in only at the end, so that its blocks do not sit on
+  // the SMs beside these for the whole scan
+  pdl_wait();
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SF_COLS;
   const int gr = h / (H / G);
   const int inner = H * P;
@@ -142,7 +144,13 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     for (int i = tid; i < n * ncol; i += SF_THREADS) y[(size_t)(first + i / ncol) * inner + h * P + col0 + i % ncol] = 0.f;
     return;
   }
-  const int stage_floats = SF_CHUNK * (2 * N + SF_COLS + 2);
+  constexpr int NP = R * SF_LANES;                      // a row of B or C in shared memory: N floats, then zeros
+  constexpr int stage_floats = SF_CHUNK * (2 * NP + SF_COLS + 2);
+  if (N < NP)                                          // (cp.async never writes the padding)
+    for (int i = tid; i < 2 * 2 * SF_CHUNK * (NP - N); i += SF_THREADS) {
+      const int row = i / (NP - N), c = i - row * (NP - N);          // row: stage, B or C, token
+      smem[(row / (2 * SF_CHUNK)) * stage_floats + (row % (2 * SF_CHUNK)) * NP + N + c] = 0.f;
+    }
   const int cl = tid / SF_LANES, part = tid % SF_LANES;
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
@@ -150,25 +158,29 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
   float S[R];
   const bool fresh = q_start[s] == 0;
+  const bool st_vec = ((uintptr_t)st % 16) == 0;       // N is a multiple of 4: then every group of 4 rows is 16-byte aligned
 #pragma unroll
-  for (int j = 0; j < R / 4; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = 4 * (part + SF_LANES * j) + e;
-      S[4 * j + e] = (live && !fresh && i < N) ? st[i] : 0.f;
+  for (int j = 0; j < R / 4; ++j) {
+    const int i = 4 * (part + SF_LANES * j);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && !fresh && i < N) {
+      if (st_vec) v = *reinterpret_cast<const float4*>(st + i);
+      else v = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
     }
+    S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+  }
 
   auto fetch = [&](int c0, int stage) {
-    float* Bs = smem + stage * stage_floats;           // [CHUNK][N]
-    float* Cs = Bs + SF_CHUNK * N;                     // [CHUNK][N]
-    float* xs = Cs + SF_CHUNK * N;                     // [CHUNK][SF_COLS]
+    float* Bs = smem + stage * stage_floats;           // [CHUNK][NP]
+    float* Cs = Bs + SF_CHUNK * NP;                    // [CHUNK][NP]
+    float* xs = Cs + SF_CHUNK * NP;                    // [CHUNK][SF_COLS]
     const int cn = min(SF_CHUNK, n - c0);
     const int n4 = N >> 2, c4 = ncol >> 2;
     for (int i = tid; i < cn * n4; i += SF_THREADS) {
       const int tt = i / n4, c = i - tt * n4;
       const float* row = xbc + (size_t)(first + c0 + tt) * xbc_stride + inner + gr * N + 4 * c;
-      ss_cp_async16(Bs + tt * N + 4 * c, row);
-      ss_cp_async16(Cs + tt * N + 4 * c, row + (size_t)G * N);
+      ss_cp_async16(Bs + tt * NP + 4 * c, row);
+      ss_cp_async16(Cs + tt * NP + 4 * c, row + (size_t)G * N);
     }
     for (int i = tid; i < cn * c4; i += SF_THREADS) {
       const int tt = i / c4, c = i - tt * c4;
@@ -188,7 +200,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     const int cn = min(SF_CHUNK, n - c0);
     if (ci + 1 < n_chunks) fetch(c0 + SF_CHUNK, stage ^ 1);
     ss_cp_async_commit();
-    float* ds = smem + stage * stage_floats + SF_CHUNK * (2 * N + SF_COLS);     // [CHUNK][2]: decay, dt
+    float* ds = smem + stage * stage_floats + SF_CHUNK * (2 * NP + SF_COLS);    // [CHUNK][2]: decay, dt
     if (tid < cn) {
       const float dt = ss_softplus(dt_next + bias);
       ds[2 * tid] = expf(-rate * dt);
@@ -198,9 +210,10 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     __syncthreads();
     if (ci + 1 < n_chunks && tid < min(SF_CHUNK, n - c0 - SF_CHUNK))
       dt_next = dt_raw[(size_t)(first + c0 + SF_CHUNK + tid) * dt_stride + h];
-    const float* Bs = smem + stage * stage_floats;
-    const float* Cs = Bs + SF_CHUNK * N;
-    const float* xs = Cs + SF_CHUNK * N;
+    const float* Bs = smem + stage * stage_floats + 4 * part;
+    const float* Cs = Bs + SF_CHUNK * NP;
+    const float* xs = smem + stage * stage_floats + 2 * SF_CHUNK * NP;
+#pragma unroll 2
     for (int tt = 0; tt < cn; ++tt) {
       const float a = ds[2 * tt], dt = ds[2 * tt + 1];
       const float xv = live ? xs[tt * SF_COLS + cl] : 0.f;
@@ -208,15 +221,12 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        const int c = part + SF_LANES * j;
-        if (4 * c < N) {
-          const float4 bb = *reinterpret_cast<const float4*>(Bs + tt * N + 4 * c);
-          const float4 cc = *reinterpret_cast<const float4*>(Cs + tt * N + 4 * c);
-          S[4 * j] = fmaf(a, S[4 * j], dx * bb.x);         acc[0] = fmaf(S[4 * j], cc.x, acc[0]);
-          S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * bb.y); acc[1] = fmaf(S[4 * j + 1], cc.y, acc[1]);
-          S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * bb.z); acc[2] = fmaf(S[4 * j + 2], cc.z, acc[2]);
-          S[4 * j + 3] = fmaf(a, S[4 * j + 3], dx * bb.w); acc[3] = fmaf(S[4 * j + 3], cc.w, acc[3]);
-        }
+        const float4 bb = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * SF_LANES * j);
+        const float4 cc = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * SF_LANES * j);
+        S[4 * j] = fmaf(a, S[4 * j], dx * bb.x);         acc[0] = fmaf(S[4 * j], cc.x, acc[0]);
+        S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * bb.y); acc[1] = fmaf(S[4 * j + 1], cc.y, acc[1]);
+        S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * bb.z); acc[2] = fmaf(S[4 * j + 2], cc.z, acc[2]);
+        S[4 * j + 3] = fmaf(a, S[4 * j + 3], dx * bb.w); acc[3] = fmaf(S[4 * j + 3], cc.w, acc[3]);
       }
       float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
@@ -226,14 +236,19 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     __syncthreads();                                   // the stage is free for the fetch after next
   }
   ss_cp_async_wait<0>();
+  pdl_launch_dependents();
   if (live) {
 #pragma unroll
-    for (int j = 0; j < R / 4; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = 4 * (part + SF_LANES * j) + e;
-        if (i < N) st[i] = S[4 * j + e];
+    for (int j = 0; j < R / 4; ++j) {
+      const int i = 4 * (part + SF_LANES * j);
+      if (i < N) {
+        if (st_vec) {
+          *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        } else {
+          st[i] = S[4 * j]; st[i + 1] = S[4 * j + 1]; st[i + 2] = S[4 * j + 2]; st[i + 3] = S[4 * j + 3];
+        }
       }
+    }
   }
 }
 
@@ -247,17 +262,18 @@ NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, c
   NHV_REQUIRE(N > 0 && N <= 256 && P > 0, "ssd_scan: a state of %d rows is beyond the supported 256", N);
   NHV_REQUIRE(state_stride >= (long)H * P * N, "ssd_scan: the state holds fewer than heads * P * N floats");
   if (dtype == NHV_F32 && N % 4 == 0 && P % 4 == 0 && xbc_stride % 4 == 0 && ((uintptr_t)xbc % 16) == 0) {
-    const size_t fsmem = (size_t)2 * SF_CHUNK * (2 * N + SF_COLS + 2) * sizeof(float);
     dim3 fgrid(n_seqs, H, (P + SF_COLS - 1) / SF_COLS);
 #define FAST(R)                                                                                                      \
   do {                                                                                                               \
     static bool attr = false;                                                                                        \
     if (!attr) {                                                                                                     \
       NHV_CUDA(cudaFuncSetAttribute(ssd_scan_fast_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
-                                    (int)((size_t)2 * SF_CHUNK * (2 * 256 + SF_COLS + 2) * sizeof(float))), "ssd_scan"); \
+                                    232448), "ssd_scan");                                                    \
       attr = true;                                                                                                   \
     }                                                                                                                \
-    nhv_launch(ssd_scan_fast_kernel<R>, fgrid, SF_THREADS, fsmem, stream, y, (const float*)xbc, xbc_stride, dt_raw,  \
+    nhv_launch(ssd_scan_fast_kernel<R>, fgrid, SF_THREADS,                                                           \
+               nhv_spread_smem((size_t)2 * SF_CHUNK * (2 * R * SF_LANES + SF_COLS + 2) * sizeof(float),             \
+                               (long)fgrid.x * fgrid.y * fgrid.z), stream, y, (const float*)xbc, xbc_stride, dt_raw,  \
                dt_stride, dt_bias, a_log, d_skip, state, state_stride, cu_q, q_start, slots, H, P, N, G);            \
   } while (0)
     if (N <= 32) FAST(4);

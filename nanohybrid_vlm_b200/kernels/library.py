@@ -34,6 +34,7 @@ _SIGNATURES = {
     "nhv_gemm_slab_geometry": [I, I, I, I, P, P, P, P, P],
     "nhv_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
     "nhv_gelu_tanh_mul": [I, P, P, I, I, P],
+    "nhv_gemm_rows_f32": [P, I, P, I, P, I, I, I, I, P],
     "nhv_embed_scaled_f32": [I, P, P, P, I, I, I, F, P],
     "nhv_rmsnorm_stream": [I, P, P, P, P, F, F, F, P, P, P, I, I, F, I, F, P],
     "nhv_scaled_sum": [I, P, P, P, F, F, c_size_t, P],

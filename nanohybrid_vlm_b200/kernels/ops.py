@@ -261,7 +261,8 @@ def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, 
 def linear_f32(out, x, weight) -> None:
     """out[M,N] float32 = x[M,K] @ weight[N,K]^T with the 32-bit sums kept (no rounding to the storage type on the
     way): small projections whose results enter a recurrence or a softmax, and heads that return exact logits.
-    float32 operands run the fixed-order kernel; bfloat16 operands the library product with a float32 result."""
+    float32 operands run the fixed-order kernel; bfloat16 operands one warp per output for few outputs, else the
+    library product with a float32 result."""
     _need_cuda(out, x, weight)
     _contig("out", out); _contig("weight", weight)
     assert x.dim() == 2 and x.stride(1) == 1 and x.dtype == weight.dtype and out.dtype == torch.float32
@@ -271,15 +272,18 @@ def linear_f32(out, x, weight) -> None:
     if x.dtype == torch.float32:
         call("nhv_gemm_nt_simt", F32, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 0,
              stream_ptr())
-    elif N * K <= LINEAR_F32_SIMT_LIMIT or not x.is_contiguous():
-        call("nhv_gemm_nt_simt", BF16, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 1,
-             stream_ptr())
-    else:
+    elif M * N <= LINEAR_F32_ROWS_LIMIT and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 \
+            and weight.data_ptr() % 16 == 0:
+        call("nhv_gemm_rows_f32", out.data_ptr(), N, x.data_ptr(), x.stride(0), weight.data_ptr(), K, M, N, K, stream_ptr())
+    elif x.is_contiguous() and M * N > LINEAR_F32_ROWS_LIMIT:
         library.LAUNCHES += 1
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    else:
+        call("nhv_gemm_nt_simt", BF16, out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, N, K, x.stride(0), K, N, 1,
+             stream_ptr())
 
 
-LINEAR_F32_SIMT_LIMIT = 1 << 19     # weight elements up to which the fixed-order CUDA-core product takes a bfloat16 matrix
+LINEAR_F32_ROWS_LIMIT = 1 << 13     # outputs up to which a bfloat16 product with float32 sums runs one warp per output
 
 
 def to_f32(out, x) -> None:

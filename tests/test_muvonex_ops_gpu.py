@@ -399,3 +399,24 @@ def test_banded_rotary_table(ops):
     f, fs = pm.rotary_frequencies(48, 5000.0, None), pm.rotary_frequencies(48, 5000.0, SCALING)
     kinds = {("kept" if a == b else "divided" if abs(a / b - 8.0) < 1e-9 else "blended") for a, b in zip(f.tolist(), fs.tolist())}
     assert kinds == {"kept", "divided", "blended"}
+
+
+# ---------------------------------------------------------------- small projections with 32-bit results
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 6, 256), (8, 32, 2048), (70, 12, 136), (3, 640, 200), (600, 40, 264), (5, 3, 36)])
+def test_linear_f32_keeps_the_sums(ops, dtype, M, N, K):
+    """x W^T with float32 sums handed on unrounded, for one row and for many, also as a view of a wider matrix; a
+    row's result does not depend on the rows beside it."""
+    g = torch.Generator().manual_seed(M + N)
+    wide = torch.randn(M, K + 8, generator=g).to(dtype)
+    w = torch.randn(N, K, generator=g).to(dtype)
+    x = dev(wide)[:, 8:] if K % 8 == 0 else dev(wide[:, 8:].contiguous())
+    out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear_f32(out, x, dev(w))
+    want = wide[:, 8:].to(F64) @ w.to(F64).T
+    torch.testing.assert_close(out.cpu().to(F64), want, rtol=1e-4, atol=1e-4 * K ** 0.5)
+    if M > 1:
+        one = torch.empty(1, N, dtype=torch.float32, device="cuda")
+        ops.linear_f32(one, x[M - 1:], dev(w))
+        if dtype == torch.float32 or M * N <= ops.LINEAR_F32_ROWS_LIMIT:
+            assert torch.equal(one[0], out[M - 1])
