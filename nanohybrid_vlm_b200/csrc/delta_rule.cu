@@ -81,10 +81,8 @@ __global__ void delta_prepare_kernel(float* __restrict__ qn, float* __restrict__
 }
 
 // ---------------------------------------------------------------- the scan for sizes in steps of 4
-constexpr int DF_COLS = 16;         // columns of S per block
-constexpr int DF_LANES = 8;         // lanes per column
 constexpr int DF_CHUNK = 16;        // tokens per stage
-constexpr int DF_THREADS = DF_COLS * DF_LANES;
+constexpr int DF_THREADS = 128;     // LANES lanes per column of S (8, 16 or 32), 128 / LANES columns per block
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
@@ -97,35 +95,36 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 // R: rows of a column per lane (a multiple of 4, R * 8 >= d).  qn, kn [T, G, d]; kq [T, G]; v32: rows of v_stride
 // floats whose first H * dv are the token's values; all fp32.
-template <int R>
+template <int R, int LANES>
 __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     float* __restrict__ o_out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ kq,
     const float* __restrict__ v32, int v_stride, const float* __restrict__ beta, const float* __restrict__ decay,
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
     const int* __restrict__ slots, int G, int H, int d, int dv) {
+  constexpr int COLS = DF_THREADS / LANES;             // columns of S per block
   extern __shared__ __align__(16) float smem[];
   // a long kernel of few blocks: the kernel behind it is let in only at the end, so that its blocks do not sit on
   // the SMs beside these for the whole scan
   pdl_wait();
-  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DF_COLS;
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
   const int g = h / (H / G);
   const int first = cu_q[s], n = cu_q[s + 1] - first;
   const int slot = slots[s];
   const int tid = threadIdx.x;
-  const int ncol = min(DF_COLS, dv - col0);            // a multiple of 4
+  const int ncol = min(COLS, dv - col0);            // a multiple of 4
   if (slot < 0) {
     for (int i = tid; i < n * ncol; i += DF_THREADS)
       o_out[((size_t)(first + i / ncol) * H + h) * dv + col0 + i % ncol] = 0.f;
     return;
   }
-  constexpr int DP = R * DF_LANES;                      // a row of q or k in shared memory: d floats, then zeros
-  constexpr int stage_floats = DF_CHUNK * (2 * DP + DF_COLS + 4);
+  constexpr int DP = R * LANES;                      // a row of q or k in shared memory: d floats, then zeros
+  constexpr int stage_floats = DF_CHUNK * (2 * DP + COLS + 4);
   if (d < DP)                                          // (cp.async never writes the padding)
     for (int i = tid; i < 2 * 2 * DF_CHUNK * (DP - d); i += DF_THREADS) {
       const int row = i / (DP - d), c = i - row * (DP - d);          // row: stage, q or k, token
       smem[(row / (2 * DF_CHUNK)) * stage_floats + (row % (2 * DF_CHUNK)) * DP + d + c] = 0.f;
     }
-  const int cl = tid / DF_LANES, part = tid % DF_LANES;
+  const int cl = tid / LANES, part = tid % LANES;
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
   float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + col) * d;
@@ -134,7 +133,7 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
   const bool st_vec = ((uintptr_t)st % 16) == 0;       // d is a multiple of 4: then every group of 4 rows is 16-byte aligned
 #pragma unroll
   for (int j = 0; j < R / 4; ++j) {
-    const int i = 4 * (part + DF_LANES * j);
+    const int i = 4 * (part + LANES * j);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live && !fresh && i < d) {
       if (st_vec) v = *reinterpret_cast<const float4*>(st + i);
@@ -146,8 +145,8 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
   auto fetch = [&](int c0, int stage) {
     float* qs = smem + stage * stage_floats;           // [CHUNK][DP]
     float* ks = qs + DF_CHUNK * DP;                    // [CHUNK][DP]
-    float* vs = ks + DF_CHUNK * DP;                    // [CHUNK][DF_COLS]
-    float* sc = vs + DF_CHUNK * DF_COLS;               // [CHUNK][4]: decay, beta, k . q
+    float* vs = ks + DF_CHUNK * DP;                    // [CHUNK][COLS]
+    float* sc = vs + DF_CHUNK * COLS;               // [CHUNK][4]: decay, beta, k . q
     const int cn = min(DF_CHUNK, n - c0);
     const int d4 = d >> 2, c4 = ncol >> 2;
     for (int i = tid; i < cn * d4; i += DF_THREADS) {
@@ -158,7 +157,7 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     }
     for (int i = tid; i < cn * c4; i += DF_THREADS) {
       const int tt = i / c4, c = i - tt * c4;
-      cp_async16(vs + tt * DF_COLS + 4 * c, v32 + (size_t)(first + c0 + tt) * v_stride + h * dv + col0 + 4 * c);
+      cp_async16(vs + tt * COLS + 4 * c, v32 + (size_t)(first + c0 + tt) * v_stride + h * dv + col0 + 4 * c);
     }
     for (int i = tid; i < cn * 3; i += DF_THREADS) {
       const int tt = i / 3, w = i - tt * 3;
@@ -179,7 +178,7 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     const float* qs = smem + stage * stage_floats + 4 * part;
     const float* ks = qs + DF_CHUNK * DP;
     const float* vs = smem + stage * stage_floats + 2 * DF_CHUNK * DP;
-    const float* sc = vs + DF_CHUNK * DF_COLS;
+    const float* sc = vs + DF_CHUNK * COLS;
     const int cn = min(DF_CHUNK, n - c0);
 #pragma unroll 2
     for (int tt = 0; tt < cn; ++tt) {
@@ -187,8 +186,8 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
       float4 kk[R / 4], qq[R / 4];
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        kk[j] = *reinterpret_cast<const float4*>(ks + tt * DP + 4 * DF_LANES * j);
-        qq[j] = *reinterpret_cast<const float4*>(qs + tt * DP + 4 * DF_LANES * j);
+        kk[j] = *reinterpret_cast<const float4*>(ks + tt * DP + 4 * LANES * j);
+        qq[j] = *reinterpret_cast<const float4*>(qs + tt * DP + 4 * LANES * j);
       }
       float ak[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -199,12 +198,19 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
         ak[3] = fmaf(S[4 * j + 3], kk[j].w, ak[3]); aq[3] = fmaf(S[4 * j + 3], qq[j].w, aq[3]);
       }
       float sk = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq = (aq[0] + aq[1]) + (aq[2] + aq[3]);
+      {
+        // two sums over the column's lanes for the price of one: neighbours swap, so that even lanes go on with
+        // S . k and odd lanes with S . q; at the end they swap back
+        const bool odd = part & 1;
+        float mine = odd ? sq : sk;
+        mine += __shfl_xor_sync(0xffffffffu, odd ? sk : sq, 1);
 #pragma unroll
-      for (int off = 1; off < DF_LANES; off <<= 1) {
-        sk += __shfl_xor_sync(0xffffffffu, sk, off);
-        sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        for (int off = 2; off < LANES; off <<= 1) mine += __shfl_xor_sync(0xffffffffu, mine, off);
+        const float theirs = __shfl_xor_sync(0xffffffffu, mine, 1);
+        sk = odd ? theirs : mine;
+        sq = odd ? mine : theirs;
       }
-      const float u = bt * ((live ? vs[tt * DF_COLS + cl] : 0.f) - gt * sk);
+      const float u = bt * ((live ? vs[tt * COLS + cl] : 0.f) - gt * sk);
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
         S[4 * j] = fmaf(kk[j].x, u, gt * S[4 * j]);
@@ -221,7 +227,7 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
   if (live) {
 #pragma unroll
     for (int j = 0; j < R / 4; ++j) {
-      const int i = 4 * (part + DF_LANES * j);
+      const int i = 4 * (part + LANES * j);
       if (i < d) {
         if (st_vec) {
           *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
@@ -324,13 +330,14 @@ __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_scan_kernel(
   }
 }
 
-// o_out [T, H, dv] fp32.  Scratch given by the caller, all fp32: qn, kn [T, G, d]; kq [T, G]; v32 [T, H, dv]; beta,
+// o_out [T, H, dv] fp32.  lanes: 8, 16 or 32 lanes per column of the state, or 0 to choose by the size of the step.
+// Scratch given by the caller, all fp32: qn, kn [T, G, d]; kq [T, G]; v32 [T, H, dv]; beta,
 // decay [T, H].
 NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_stride, const float* ba,
                            const float* a_log, const float* dt_bias, float* state, long state_stride, float* qn,
                            float* kn, float* kq, float* v32, float* beta, float* decay, const int* cu_q,
                            const int* q_start, const int* slots, int n_seqs, int n_tokens, int G, int H, int d, int dv,
-                           cudaStream_t stream) {
+                           int lanes, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(G > 0 && H > 0 && H % G == 0, "delta_rule: %d heads do not divide into %d q/k heads", H, G);
   NHV_REQUIRE(d > 0 && d <= 256 && dv > 0, "delta_rule: a q/k head of %d is beyond the supported 256", d);
@@ -351,25 +358,44 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
   else NHV_REQUIRE(false, "delta_rule: unknown dtype %d", dtype);
 #undef PREP
   if (fast) {
-    dim3 grid(n_seqs, H, (dv + DF_COLS - 1) / DF_COLS);
-#define FAST(R)                                                                                                      \
+    // lanes per column: 8 measured fastest for one long request (244 ns a token against 254 with 16 lanes and 299
+    // with 32: the shuffle rounds of the sum over lanes are the longest stretch of a token's chain) and for full
+    // batches (fewest instructions in all); 16 and 32 stay for the tests
+    if (lanes != 8 && lanes != 16 && lanes != 32) lanes = 8;
+    const int cols = DF_THREADS / lanes;
+    dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
+    const int need = (d + lanes - 1) / lanes;                                // rows per lane, then rounded up to 4, 8, 16, 32
+#define FAST(R, L)                                                                                                   \
   do {                                                                                                               \
     static bool attr = false;                                                                                        \
     if (!attr) {                                                                                                     \
-      NHV_CUDA(cudaFuncSetAttribute(delta_scan_fast_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
-                                    232448), "delta_rule");                                                  \
+      NHV_CUDA(cudaFuncSetAttribute(delta_scan_fast_kernel<R, L>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                    232448), "delta_rule");                                                          \
       attr = true;                                                                                                   \
     }                                                                                                                \
-    nhv_launch(delta_scan_fast_kernel<R>, grid, DF_THREADS,                                                          \
-               nhv_spread_smem((size_t)2 * DF_CHUNK * (2 * R * DF_LANES + DF_COLS + 4) * sizeof(float),             \
-                               (long)grid.x * grid.y * grid.z), stream, o_out, (const float*)qn, (const float*)kn, \
-               (const float*)kq, v_src, v_stride, (const float*)beta, (const float*)decay, state, state_stride,     \
-               cu_q, q_start, slots, G, H, d, dv);                                                                   \
+    nhv_launch(delta_scan_fast_kernel<R, L>, grid, DF_THREADS,                                                       \
+               nhv_spread_smem((size_t)2 * DF_CHUNK * (2 * R * L + DF_THREADS / L + 4) * sizeof(float),              \
+                               (long)grid.x * grid.y * grid.z), stream,                                             \
+               o_out, (const float*)qn, (const float*)kn, (const float*)kq, v_src, v_stride, (const float*)beta,    \
+               (const float*)decay, state, state_stride, cu_q, q_start, slots, G, H, d, dv);                        \
   } while (0)
-    if (d <= 32) FAST(4);
-    else if (d <= 64) FAST(8);
-    else if (d <= 128) FAST(16);
-    else FAST(32);
+#define FAST_L(L)                          \
+  do {                                     \
+    if (need <= 4) FAST(4, L);             \
+    else if (need <= 8) FAST(8, L);        \
+    else if (need <= 16) FAST(16, L);      \
+    else FAST(32, L);                      \
+  } while (0)
+    if (lanes == 8) FAST_L(8);
+    else if (lanes == 16) {
+      if (need <= 4) FAST(4, 16);
+      else if (need <= 8) FAST(8, 16);
+      else FAST(16, 16);
+    } else {
+      if (need <= 4) FAST(4, 32);
+      else FAST(8, 32);
+    }
+#undef FAST_L
 #undef FAST
   } else {
     const int rows = (d + DR_PARTS - 1) / DR_PARTS;

@@ -112,10 +112,8 @@ __global__ void __launch_bounds__(SS_COLS * SS_PARTS) ssd_scan_kernel(
 
 
 // ---------------------------------------------------------------- the scan for fp32 inputs and sizes in steps of 4
-constexpr int SF_COLS = 16;
-constexpr int SF_LANES = 8;
-constexpr int SF_CHUNK = 16;
-constexpr int SF_THREADS = SF_COLS * SF_LANES;
+constexpr int SF_CHUNK = 16;        // tokens per stage
+constexpr int SF_THREADS = 128;     // LANES lanes per column of S (8, 16 or 32), 128 / LANES columns per block
 
 __device__ __forceinline__ void ss_cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
@@ -123,35 +121,36 @@ __device__ __forceinline__ void ss_cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void ss_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N_> __device__ __forceinline__ void ss_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N_)); }
 
-template <int R>
+template <int R, int LANES>
 __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     float* __restrict__ y, const float* __restrict__ xbc, int xbc_stride, const float* __restrict__ dt_raw, int dt_stride,
     const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
     float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
     const int* __restrict__ slots, int H, int P, int N, int G) {
+  constexpr int COLS = SF_THREADS / LANES;             // columns of S per block
   extern __shared__ __align__(16) float smem[];
   // a long kernel of few blocks: the kernel behind it is let in only at the end, so that its blocks do not sit on
   // the SMs beside these for the whole scan
   pdl_wait();
-  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SF_COLS;
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
   const int gr = h / (H / G);
   const int inner = H * P;
   const int first = cu_q[s], n = cu_q[s + 1] - first;
   const int slot = slots[s];
   const int tid = threadIdx.x;
-  const int ncol = min(SF_COLS, P - col0);             // a multiple of 4
+  const int ncol = min(COLS, P - col0);             // a multiple of 4
   if (slot < 0) {
     for (int i = tid; i < n * ncol; i += SF_THREADS) y[(size_t)(first + i / ncol) * inner + h * P + col0 + i % ncol] = 0.f;
     return;
   }
-  constexpr int NP = R * SF_LANES;                      // a row of B or C in shared memory: N floats, then zeros
-  constexpr int stage_floats = SF_CHUNK * (2 * NP + SF_COLS + 2);
+  constexpr int NP = R * LANES;                      // a row of B or C in shared memory: N floats, then zeros
+  constexpr int stage_floats = SF_CHUNK * (2 * NP + COLS + 2);
   if (N < NP)                                          // (cp.async never writes the padding)
     for (int i = tid; i < 2 * 2 * SF_CHUNK * (NP - N); i += SF_THREADS) {
       const int row = i / (NP - N), c = i - row * (NP - N);          // row: stage, B or C, token
       smem[(row / (2 * SF_CHUNK)) * stage_floats + (row % (2 * SF_CHUNK)) * NP + N + c] = 0.f;
     }
-  const int cl = tid / SF_LANES, part = tid % SF_LANES;
+  const int cl = tid / LANES, part = tid % LANES;
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
   float* st = state + (size_t)slot * state_stride + ((size_t)h * P + col) * N;
@@ -161,7 +160,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   const bool st_vec = ((uintptr_t)st % 16) == 0;       // N is a multiple of 4: then every group of 4 rows is 16-byte aligned
 #pragma unroll
   for (int j = 0; j < R / 4; ++j) {
-    const int i = 4 * (part + SF_LANES * j);
+    const int i = 4 * (part + LANES * j);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live && !fresh && i < N) {
       if (st_vec) v = *reinterpret_cast<const float4*>(st + i);
@@ -173,7 +172,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   auto fetch = [&](int c0, int stage) {
     float* Bs = smem + stage * stage_floats;           // [CHUNK][NP]
     float* Cs = Bs + SF_CHUNK * NP;                    // [CHUNK][NP]
-    float* xs = Cs + SF_CHUNK * NP;                    // [CHUNK][SF_COLS]
+    float* xs = Cs + SF_CHUNK * NP;                    // [CHUNK][COLS]
     const int cn = min(SF_CHUNK, n - c0);
     const int n4 = N >> 2, c4 = ncol >> 2;
     for (int i = tid; i < cn * n4; i += SF_THREADS) {
@@ -184,7 +183,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     }
     for (int i = tid; i < cn * c4; i += SF_THREADS) {
       const int tt = i / c4, c = i - tt * c4;
-      ss_cp_async16(xs + tt * SF_COLS + 4 * c, xbc + (size_t)(first + c0 + tt) * xbc_stride + h * P + col0 + 4 * c);
+      ss_cp_async16(xs + tt * COLS + 4 * c, xbc + (size_t)(first + c0 + tt) * xbc_stride + h * P + col0 + 4 * c);
     }
   };
 
@@ -200,7 +199,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     const int cn = min(SF_CHUNK, n - c0);
     if (ci + 1 < n_chunks) fetch(c0 + SF_CHUNK, stage ^ 1);
     ss_cp_async_commit();
-    float* ds = smem + stage * stage_floats + SF_CHUNK * (2 * NP + SF_COLS);    // [CHUNK][2]: decay, dt
+    float* ds = smem + stage * stage_floats + SF_CHUNK * (2 * NP + COLS);    // [CHUNK][2]: decay, dt
     if (tid < cn) {
       const float dt = ss_softplus(dt_next + bias);
       ds[2 * tid] = expf(-rate * dt);
@@ -216,13 +215,13 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
 #pragma unroll 2
     for (int tt = 0; tt < cn; ++tt) {
       const float a = ds[2 * tt], dt = ds[2 * tt + 1];
-      const float xv = live ? xs[tt * SF_COLS + cl] : 0.f;
+      const float xv = live ? xs[tt * COLS + cl] : 0.f;
       const float dx = dt * xv;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        const float4 bb = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * SF_LANES * j);
-        const float4 cc = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * SF_LANES * j);
+        const float4 bb = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * LANES * j);
+        const float4 cc = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * LANES * j);
         S[4 * j] = fmaf(a, S[4 * j], dx * bb.x);         acc[0] = fmaf(S[4 * j], cc.x, acc[0]);
         S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * bb.y); acc[1] = fmaf(S[4 * j + 1], cc.y, acc[1]);
         S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * bb.z); acc[2] = fmaf(S[4 * j + 2], cc.z, acc[2]);
@@ -230,7 +229,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
       }
       float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
-      for (int off = 1; off < SF_LANES; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      for (int off = 1; off < LANES; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
       if (live && part == 0) y[(size_t)(first + c0 + tt) * inner + h * P + col] = fmaf(skip, xv, sum);
     }
     __syncthreads();                                   // the stage is free for the fetch after next
@@ -240,7 +239,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   if (live) {
 #pragma unroll
     for (int j = 0; j < R / 4; ++j) {
-      const int i = 4 * (part + SF_LANES * j);
+      const int i = 4 * (part + LANES * j);
       if (i < N) {
         if (st_vec) {
           *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
@@ -252,34 +251,51 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   }
 }
 
-// xbc [T, H*P + 2*G*N] (x, then B, then C), dt_raw [T, >= H] fp32, y [T, H*P] fp32
+// xbc [T, H*P + 2*G*N] (x, then B, then C), dt_raw [T, >= H] fp32, y [T, H*P] fp32.  lanes: 8, 16 or 32 lanes per
+// column of the state in the fast form, or 0 to choose by the size of the step.
 NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, const float* dt_raw, int dt_stride,
                          const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                          long state_stride, const int* cu_q, const int* q_start, const int* slots, int n_seqs,
-                         int n_tokens, int H, int P, int N, int G, cudaStream_t stream) {
+                         int n_tokens, int H, int P, int N, int G, int lanes, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(G > 0 && H > 0 && H % G == 0, "ssd_scan: %d heads do not divide into %d groups", H, G);
   NHV_REQUIRE(N > 0 && N <= 256 && P > 0, "ssd_scan: a state of %d rows is beyond the supported 256", N);
   NHV_REQUIRE(state_stride >= (long)H * P * N, "ssd_scan: the state holds fewer than heads * P * N floats");
   if (dtype == NHV_F32 && N % 4 == 0 && P % 4 == 0 && xbc_stride % 4 == 0 && ((uintptr_t)xbc % 16) == 0) {
-    dim3 fgrid(n_seqs, H, (P + SF_COLS - 1) / SF_COLS);
-#define FAST(R)                                                                                                      \
+    // lanes per column: 8 measured fastest for one long request (244 ns a token against 254 with 16 lanes and 299
+    // with 32: the shuffle rounds of the sum over lanes are the longest stretch of a token's chain) and for full
+    // batches (fewest instructions in all); 16 and 32 stay for the tests
+    if (lanes != 8 && lanes != 16 && lanes != 32) lanes = 8;
+    const int cols = SF_THREADS / lanes;
+    dim3 fgrid(n_seqs, H, (P + cols - 1) / cols);
+    const int need = (N + lanes - 1) / lanes;
+#define FAST(R, L)                                                                                                   \
   do {                                                                                                               \
     static bool attr = false;                                                                                        \
     if (!attr) {                                                                                                     \
-      NHV_CUDA(cudaFuncSetAttribute(ssd_scan_fast_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
-                                    232448), "ssd_scan");                                                    \
+      NHV_CUDA(cudaFuncSetAttribute(ssd_scan_fast_kernel<R, L>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                    232448), "ssd_scan");                                                            \
       attr = true;                                                                                                   \
     }                                                                                                                \
-    nhv_launch(ssd_scan_fast_kernel<R>, fgrid, SF_THREADS,                                                           \
-               nhv_spread_smem((size_t)2 * SF_CHUNK * (2 * R * SF_LANES + SF_COLS + 2) * sizeof(float),             \
-                               (long)fgrid.x * fgrid.y * fgrid.z), stream, y, (const float*)xbc, xbc_stride, dt_raw,  \
-               dt_stride, dt_bias, a_log, d_skip, state, state_stride, cu_q, q_start, slots, H, P, N, G);            \
+    nhv_launch(ssd_scan_fast_kernel<R, L>, fgrid, SF_THREADS,                                                        \
+               nhv_spread_smem((size_t)2 * SF_CHUNK * (2 * R * L + SF_THREADS / L + 2) * sizeof(float),              \
+                               (long)fgrid.x * fgrid.y * fgrid.z), stream,                                          \
+               y, (const float*)xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, d_skip, state, state_stride,    \
+               cu_q, q_start, slots, H, P, N, G);                                                                    \
   } while (0)
-    if (N <= 32) FAST(4);
-    else if (N <= 64) FAST(8);
-    else if (N <= 128) FAST(16);
-    else FAST(32);
+    if (lanes == 8) {
+      if (need <= 4) FAST(4, 8);
+      else if (need <= 8) FAST(8, 8);
+      else if (need <= 16) FAST(16, 8);
+      else FAST(32, 8);
+    } else if (lanes == 16) {
+      if (need <= 4) FAST(4, 16);
+      else if (need <= 8) FAST(8, 16);
+      else FAST(16, 16);
+    } else {
+      if (need <= 4) FAST(4, 32);
+      else FAST(8, 32);
+    }
 #undef FAST
     NHV_CHECK_LAUNCH("ssd_scan");
     return 0;
@@ -336,11 +352,67 @@ __global__ void gated_rmsnorm_kernel(T* __restrict__ out, int out_stride, const 
   }
 }
 
+// One warp per (token, group), for groups of up to 256 elements (a head of the delta rule): no barrier, the group's values stay in registers
+// between the sum of squares and the output.
+constexpr int GN_WARPS = 8;
+constexpr int GN_MAX = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(GN_WARPS * 32) gated_rmsnorm_warp_kernel(
+    T* __restrict__ out, int out_stride, const float* __restrict__ y, const T* __restrict__ z, int z_stride,
+    const T* __restrict__ w, int w_period, long n_items, int n_groups, int size, float eps, int gate_first) {
+  pdl_prologue();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * GN_WARPS + warp;
+  if (item >= n_items) return;
+  const long t = item / n_groups;
+  const int gidx = (int)(item - t * n_groups);
+  const float* yr = y + (size_t)item * size;
+  const T* zr = z + (size_t)t * z_stride + (size_t)gidx * size;
+  T* dst = out + (size_t)t * out_stride + (size_t)gidx * size;
+  float vals[GN_MAX / 32], gates[GN_MAX / 32];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < GN_MAX / 32; ++k) {
+    const int c = lane + k * 32;
+    if (c < size) {
+      const float g = to_f32<T>(zr[c]);
+      const float sg = g / (1.0f + expf(-g));
+      const float v = gate_first ? yr[c] * sg : yr[c];
+      vals[k] = v;
+      gates[k] = gate_first ? 1.0f : sg;
+      ss = fmaf(v, v, ss);
+    }
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)size + eps);
+#pragma unroll
+  for (int k = 0; k < GN_MAX / 32; ++k) {
+    const int c = lane + k * 32;
+    if (c < size) dst[c] = from_f32<T>(vals[k] * gates[k] * rstd * to_f32<T>(w[(gidx * size + c) % w_period]));
+  }
+}
+
 NHV_API int nhv_gated_rmsnorm(int dtype, void* out, int out_stride, const float* y, const void* z, int z_stride,
                               const void* w, int w_period, int n_tokens, int n_groups, int size, float eps,
                               int gate_first, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(n_groups > 0 && size > 0 && w_period > 0, "gated_rmsnorm: bad sizes");
+  if (size <= GN_MAX) {           // larger groups: a block per (token, group) below
+    const long items = (long)n_tokens * n_groups;
+    const long wblocks = (items + GN_WARPS - 1) / GN_WARPS;
+    NHV_REQUIRE(wblocks < (1L << 31), "gated_rmsnorm: too many rows");
+    if (dtype == NHV_F32)
+      nhv_launch(gated_rmsnorm_warp_kernel<float>, (int)wblocks, GN_WARPS * 32, 0, stream, (float*)out, out_stride, y,
+                 (const float*)z, z_stride, (const float*)w, w_period, items, n_groups, size, eps, gate_first);
+    else if (dtype == NHV_BF16)
+      nhv_launch(gated_rmsnorm_warp_kernel<__nv_bfloat16>, (int)wblocks, GN_WARPS * 32, 0, stream, (__nv_bfloat16*)out,
+                 out_stride, y, (const __nv_bfloat16*)z, z_stride, (const __nv_bfloat16*)w, w_period, items, n_groups, size,
+                 eps, gate_first);
+    else
+      NHV_REQUIRE(false, "gated_rmsnorm: unknown dtype %d", dtype);
+    NHV_CHECK_LAUNCH("gated_rmsnorm");
+    return 0;
+  }
   int threads = 32;
   while (threads < 256 && threads * 2 <= size) threads <<= 1;
   const long blocks = (long)n_tokens * n_groups;

@@ -158,6 +158,9 @@ def short_conv_silu(out, x, weight, bias, state, batch) -> None:
          batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
 
 
+SCAN_LANES = 0      # lanes per state column in the recurrent scans: 0 chooses by the size of the step; tests set 8, 16, 32
+
+
 def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int, dv: int) -> None:
     """The gated delta rule over the step's tokens.  qkv [T, 2*G*d + H*dv] (q, k, v after their convolutions), ba
     [T, 2*H] float32 (inputs of beta's sigmoid, then of the decay's softplus), a_log / dt_bias [H] float32, state
@@ -175,7 +178,7 @@ def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int,
     qn, kn, v32, kq, beta, decay = ptrs
     call("nhv_delta_rule", dtype_code(qkv), o.data_ptr(), qkv.data_ptr(), qkv.stride(0), ba.data_ptr(), a_log.data_ptr(),
          dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qn, kn, kq, v32, beta, decay, batch.cu_q.data_ptr(),
-         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, stream_ptr())
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, SCAN_LANES, stream_ptr())
 
 
 def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: int, N: int, G: int) -> None:
@@ -188,7 +191,7 @@ def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: in
     assert y.is_contiguous() and y.shape == (T, H * P)
     call("nhv_ssd_scan", dtype_code(xbc), y.data_ptr(), xbc.data_ptr(), xbc.stride(0), dt_raw.data_ptr(), dt_raw.stride(0),
          dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(),
-         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, P, N, G, stream_ptr())
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, P, N, G, SCAN_LANES, stream_ptr())
 
 
 def gated_rmsnorm(out, y, z, weight, n_groups: int, eps: float, gate_first: bool) -> None:

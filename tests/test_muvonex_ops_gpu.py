@@ -108,10 +108,18 @@ def plain_delta(qkv, ba, a_log, dt_bias, G, H, d, dv):
     return pm.delta_recurrence(q, k, v, beta, decay).reshape(T, H * dv)
 
 
+@pytest.fixture(params=[0, 8, 16, 32])
+def lanes(request, ops):
+    """Every way of laying a state column over lanes (0: chosen by the size of the step)."""
+    ops.SCAN_LANES = request.param
+    yield request.param
+    ops.SCAN_LANES = 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("G,H,d,dv", [(2, 4, 24, 40), (3, 3, 48, 16), (1, 5, 100, 72), (2, 2, 16, 130), (1, 1, 256, 8),
                                       (2, 2, 30, 18), (1, 2, 128, 128), (1, 3, 7, 5)])
-def test_delta_rule_over_portions_and_reused_slots(ops, dtype, G, H, d, dv):
+def test_delta_rule_over_portions_and_reused_slots(ops, lanes, dtype, G, H, d, dv):
     g = torch.Generator().manual_seed(G * 1000 + d)
     lengths, cuts, slots = [41, 19, 6], [[2, 3, 20, 37], [18], [1, 2, 3, 4, 5]], [1, 3, 0]
     ins = [delta_inputs(g, L, G, H, d, dv, dtype) for L in lengths]
@@ -143,7 +151,7 @@ def test_delta_rule_over_portions_and_reused_slots(ops, dtype, G, H, d, dv):
     assert torch.equal(torch.nan_to_num(state[keep]), torch.nan_to_num(before[keep]))
 
 
-def test_delta_rule_recalls_a_value_written_long_ago(ops):
+def test_delta_rule_recalls_a_value_written_long_ago(ops, lanes):
     """With beta = 1 and no decay the state is an associative memory: the value written under one key hundreds of
     tokens back (in an earlier portion) comes out again for a query along that key, and a later write under the
     same key replaces it.  Keys in between are orthogonal to it."""
@@ -188,7 +196,7 @@ def plain_ssd(xbc, dt_raw, dt_bias, a_log, skip, H, P, N, G):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,P,N,G", [(4, 24, 16, 2), (6, 40, 48, 3), (3, 130, 20, 1), (2, 8, 256, 2), (5, 64, 7, 5),
                                      (2, 64, 128, 1), (3, 20, 100, 3)])
-def test_ssd_scan_over_portions_and_reused_slots(ops, dtype, H, P, N, G):
+def test_ssd_scan_over_portions_and_reused_slots(ops, lanes, dtype, H, P, N, G):
     g = torch.Generator().manual_seed(H * 100 + N)
     lengths, cuts, slots = [37, 12, 5], [[2, 3, 19, 36], [11], [1, 2, 3, 4]], [3, 0, 2]
     dt_bias, a_log = torch.randn(H, generator=g) * 0.5, torch.rand(H, generator=g) * 1.5 - 1.0
@@ -218,7 +226,7 @@ def test_ssd_scan_over_portions_and_reused_slots(ops, dtype, H, P, N, G):
     assert torch.equal(y[3:].cpu(), torch.zeros(3, H * P))
 
 
-def test_ssd_scan_keeps_an_input_from_long_ago(ops):
+def test_ssd_scan_keeps_an_input_from_long_ago(ops, lanes):
     """With a decay of almost one the state still holds the first token's write after 400 tokens whose B is
     orthogonal to the last C: the output is dt_0 x_0 (B_0 . C_last), through a portion's edge and single tokens."""
     H, P, N, G, T = 1, 16, 32, 1, 400
