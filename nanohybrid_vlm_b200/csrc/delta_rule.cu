@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
   float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + col) * d;
-  float S[R];
+  f32x2 S[R / 2];                                      // rows 4c, 4c+1 | 4c+2, 4c+3 of the lane's groups of four
   const bool fresh = q_start[s] == 0;
   const bool st_vec = ((uintptr_t)st % 16) == 0;       // d is a multiple of 4: then every group of 4 rows is 16-byte aligned
 #pragma unroll
@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
       if (st_vec) v = *reinterpret_cast<const float4*>(st + i);
       else v = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
     }
-    S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+    S[2 * j] = f2_pack(v.x, v.y);
+    S[2 * j + 1] = f2_pack(v.z, v.w);
   }
 
   auto fetch = [&](int c0, int stage) {
@@ -180,24 +181,40 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     const float* vs = smem + stage * stage_floats + 2 * DF_CHUNK * DP;
     const float* sc = vs + DF_CHUNK * COLS;
     const int cn = min(DF_CHUNK, n - c0);
-#pragma unroll 2
+    // a token's k, q, v and scalars are read from shared memory one token ahead, so that the reads are under
+    // way while the token before goes through its shuffles
+    ulonglong2 kk[R / 4], qq[R / 4], kk_n[R / 4], qq_n[R / 4];      // four floats as two pairs
+    float4 sc_n = *reinterpret_cast<const float4*>(sc);
+    float v_n = live ? vs[cl] : 0.f;
+#pragma unroll
+    for (int j = 0; j < R / 4; ++j) {
+      kk_n[j] = *reinterpret_cast<const ulonglong2*>(ks + 4 * LANES * j);
+      qq_n[j] = *reinterpret_cast<const ulonglong2*>(qs + 4 * LANES * j);
+    }
     for (int tt = 0; tt < cn; ++tt) {
-      const float gt = sc[tt * 4], bt = sc[tt * 4 + 1], kqt = sc[tt * 4 + 2];
-      float4 kk[R / 4], qq[R / 4];
+      const float gt = sc_n.x, bt = sc_n.y, kqt = sc_n.z, vt = v_n;
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        kk[j] = *reinterpret_cast<const float4*>(ks + tt * DP + 4 * LANES * j);
-        qq[j] = *reinterpret_cast<const float4*>(qs + tt * DP + 4 * LANES * j);
+        kk[j] = kk_n[j];
+        qq[j] = qq_n[j];
       }
-      float ak[4] = {0.f, 0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const int tn = min(tt + 1, DF_CHUNK - 1);      // (the row behind the last token of a short chunk holds old data: read, not used)
+        sc_n = *reinterpret_cast<const float4*>(sc + tn * 4);
+        v_n = live ? vs[tn * COLS + cl] : 0.f;
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          kk_n[j] = *reinterpret_cast<const ulonglong2*>(ks + tn * DP + 4 * LANES * j);
+          qq_n[j] = *reinterpret_cast<const ulonglong2*>(qs + tn * DP + 4 * LANES * j);
+        }
+      }
+      f32x2 ak[2] = {0ull, 0ull}, aq[2] = {0ull, 0ull};
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        ak[0] = fmaf(S[4 * j], kk[j].x, ak[0]);     aq[0] = fmaf(S[4 * j], qq[j].x, aq[0]);
-        ak[1] = fmaf(S[4 * j + 1], kk[j].y, ak[1]); aq[1] = fmaf(S[4 * j + 1], qq[j].y, aq[1]);
-        ak[2] = fmaf(S[4 * j + 2], kk[j].z, ak[2]); aq[2] = fmaf(S[4 * j + 2], qq[j].z, aq[2]);
-        ak[3] = fmaf(S[4 * j + 3], kk[j].w, ak[3]); aq[3] = fmaf(S[4 * j + 3], qq[j].w, aq[3]);
+        ak[0] = f2_fma(S[2 * j], kk[j].x, ak[0]);     aq[0] = f2_fma(S[2 * j], qq[j].x, aq[0]);
+        ak[1] = f2_fma(S[2 * j + 1], kk[j].y, ak[1]); aq[1] = f2_fma(S[2 * j + 1], qq[j].y, aq[1]);
       }
-      float sk = (ak[0] + ak[1]) + (ak[2] + ak[3]), sq = (aq[0] + aq[1]) + (aq[2] + aq[3]);
+      float sk = f2_sum(ak[0], ak[1]), sq = f2_sum(aq[0], aq[1]);
       {
         // two sums over the column's lanes for the price of one: neighbours swap, so that even lanes go on with
         // S . k and odd lanes with S . q; at the end they swap back
@@ -210,13 +227,12 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
         sk = odd ? theirs : mine;
         sq = odd ? mine : theirs;
       }
-      const float u = bt * ((live ? vs[tt * COLS + cl] : 0.f) - gt * sk);
+      const float u = bt * (vt - gt * sk);
+      const f32x2 uu = f2_pack(u, u), gg = f2_pack(gt, gt);
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        S[4 * j] = fmaf(kk[j].x, u, gt * S[4 * j]);
-        S[4 * j + 1] = fmaf(kk[j].y, u, gt * S[4 * j + 1]);
-        S[4 * j + 2] = fmaf(kk[j].z, u, gt * S[4 * j + 2]);
-        S[4 * j + 3] = fmaf(kk[j].w, u, gt * S[4 * j + 3]);
+        S[2 * j] = f2_fma(kk[j].x, uu, f2_mul(S[2 * j], gg));
+        S[2 * j + 1] = f2_fma(kk[j].y, uu, f2_mul(S[2 * j + 1], gg));
       }
       if (live && part == 0) o_out[((size_t)(first + c0 + tt) * H + h) * dv + col] = fmaf(u, kqt, gt * sq);
     }
@@ -229,10 +245,13 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_fast_kernel(
     for (int j = 0; j < R / 4; ++j) {
       const int i = 4 * (part + LANES * j);
       if (i < d) {
+        float4 v;
+        f2_unpack(S[2 * j], v.x, v.y);
+        f2_unpack(S[2 * j + 1], v.z, v.w);
         if (st_vec) {
-          *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+          *reinterpret_cast<float4*>(st + i) = v;
         } else {
-          st[i] = S[4 * j]; st[i + 1] = S[4 * j + 1]; st[i + 2] = S[4 * j + 2]; st[i + 3] = S[4 * j + 3];
+          st[i] = v.x; st[i + 1] = v.y; st[i + 2] = v.z; st[i + 3] = v.w;
         }
       }
     }
@@ -361,7 +380,8 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
     // lanes per column: 8 measured fastest for one long request (244 ns a token against 254 with 16 lanes and 299
     // with 32: the shuffle rounds of the sum over lanes are the longest stretch of a token's chain) and for full
     // batches (fewest instructions in all); 16 and 32 stay for the tests
-    if (lanes != 8 && lanes != 16 && lanes != 32) lanes = 8;
+    if (lanes != 4 && lanes != 8 && lanes != 16 && lanes != 32) lanes = 8;
+    if (lanes == 4 && d > 128) lanes = 8;                                    // 4 lanes hold at most 32 rows each
     const int cols = DF_THREADS / lanes;
     dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
     const int need = (d + lanes - 1) / lanes;                                // rows per lane, then rounded up to 4, 8, 16, 32
@@ -386,7 +406,8 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
     else if (need <= 16) FAST(16, L);      \
     else FAST(32, L);                      \
   } while (0)
-    if (lanes == 8) FAST_L(8);
+    if (lanes == 4) FAST_L(4);
+    else if (lanes == 8) FAST_L(8);
     else if (lanes == 16) {
       if (need <= 4) FAST(4, 16);
       else if (need <= 8) FAST(8, 16);

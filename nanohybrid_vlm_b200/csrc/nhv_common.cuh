@@ -99,6 +99,32 @@ inline size_t nhv_spread_smem(size_t need, long blocks, int sms = 148) {
   return want > need ? want : need;
 }
 
+// Two fp32 values in one 64-bit register and the arithmetic on both at once (sm_100: one instruction does two
+// fused multiply-adds, each rounded as the scalar one is).  A 16-byte read of four floats is two such pairs.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float f2_sum(f32x2 a, f32x2 b) {     // (a.lo + a.hi) + (b.lo + b.hi)
+  float x, y, z, w;
+  f2_unpack(a, x, y);
+  f2_unpack(b, z, w);
+  return (x + y) + (z + w);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   const int col = col0 + (live ? cl : 0);
   float* st = state + (size_t)slot * state_stride + ((size_t)h * P + col) * N;
   const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
-  float S[R];
+  f32x2 S[R / 2];                                      // rows 4c, 4c+1 | 4c+2, 4c+3 of the lane's groups of four
   const bool fresh = q_start[s] == 0;
   const bool st_vec = ((uintptr_t)st % 16) == 0;       // N is a multiple of 4: then every group of 4 rows is 16-byte aligned
 #pragma unroll
@@ -166,7 +166,8 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
       if (st_vec) v = *reinterpret_cast<const float4*>(st + i);
       else v = make_float4(st[i], st[i + 1], st[i + 2], st[i + 3]);
     }
-    S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+    S[2 * j] = f2_pack(v.x, v.y);
+    S[2 * j + 1] = f2_pack(v.z, v.w);
   }
 
   auto fetch = [&](int c0, int stage) {
@@ -217,17 +218,16 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
       const float a = ds[2 * tt], dt = ds[2 * tt + 1];
       const float xv = live ? xs[tt * COLS + cl] : 0.f;
       const float dx = dt * xv;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const f32x2 aa = f2_pack(a, a), dd = f2_pack(dx, dx);
+      f32x2 acc[2] = {0ull, 0ull};
 #pragma unroll
       for (int j = 0; j < R / 4; ++j) {
-        const float4 bb = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * LANES * j);
-        const float4 cc = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * LANES * j);
-        S[4 * j] = fmaf(a, S[4 * j], dx * bb.x);         acc[0] = fmaf(S[4 * j], cc.x, acc[0]);
-        S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * bb.y); acc[1] = fmaf(S[4 * j + 1], cc.y, acc[1]);
-        S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * bb.z); acc[2] = fmaf(S[4 * j + 2], cc.z, acc[2]);
-        S[4 * j + 3] = fmaf(a, S[4 * j + 3], dx * bb.w); acc[3] = fmaf(S[4 * j + 3], cc.w, acc[3]);
+        const ulonglong2 bb = *reinterpret_cast<const ulonglong2*>(Bs + tt * NP + 4 * LANES * j);   // four floats, two pairs
+        const ulonglong2 cc = *reinterpret_cast<const ulonglong2*>(Cs + tt * NP + 4 * LANES * j);
+        S[2 * j] = f2_fma(aa, S[2 * j], f2_mul(dd, bb.x));         acc[0] = f2_fma(S[2 * j], cc.x, acc[0]);
+        S[2 * j + 1] = f2_fma(aa, S[2 * j + 1], f2_mul(dd, bb.y)); acc[1] = f2_fma(S[2 * j + 1], cc.y, acc[1]);
       }
-      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      float sum = f2_sum(acc[0], acc[1]);
 #pragma unroll
       for (int off = 1; off < LANES; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
       if (live && part == 0) y[(size_t)(first + c0 + tt) * inner + h * P + col] = fmaf(skip, xv, sum);
@@ -241,10 +241,13 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
     for (int j = 0; j < R / 4; ++j) {
       const int i = 4 * (part + LANES * j);
       if (i < N) {
+        float4 v;
+        f2_unpack(S[2 * j], v.x, v.y);
+        f2_unpack(S[2 * j + 1], v.z, v.w);
         if (st_vec) {
-          *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+          *reinterpret_cast<float4*>(st + i) = v;
         } else {
-          st[i] = S[4 * j]; st[i + 1] = S[4 * j + 1]; st[i + 2] = S[4 * j + 2]; st[i + 3] = S[4 * j + 3];
+          st[i] = v.x; st[i + 1] = v.y; st[i + 2] = v.z; st[i + 3] = v.w;
         }
       }
     }

@@ -158,7 +158,7 @@ def short_conv_silu(out, x, weight, bias, state, batch) -> None:
          batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
 
 
-SCAN_LANES = 0      # lanes per state column in the recurrent scans: 0 chooses by the size of the step; tests set 8, 16, 32
+SCAN_LANES = 0      # lanes per state column in the recurrent scans: 0 is the kernels' own choice; tests set 4, 8, 16, 32
 
 
 def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int, dv: int) -> None:

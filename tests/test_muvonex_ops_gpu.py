@@ -108,7 +108,7 @@ def plain_delta(qkv, ba, a_log, dt_bias, G, H, d, dv):
     return pm.delta_recurrence(q, k, v, beta, decay).reshape(T, H * dv)
 
 
-@pytest.fixture(params=[0, 8, 16, 32])
+@pytest.fixture(params=[0, 4, 8, 16, 32])
 def lanes(request, ops):
     """Every way of laying a state column over lanes (0: chosen by the size of the step)."""
     ops.SCAN_LANES = request.param
