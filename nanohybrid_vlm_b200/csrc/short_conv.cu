@@ -10,7 +10,7 @@
 #include "nhv_common.cuh"
 
 constexpr int SC_MAX_TAPS = 8;
-constexpr int SC_TOKENS = 8;        // tokens per block of the output kernel in a long step (the filters are read once for them);
+constexpr int SC_TOKENS = 32;       // tokens per block of the output kernel in a long step (each input is read once for them);
                                     // a short step takes one token per block: finding a token's request is a chain of
                                     // dependent loads that the tokens of a block would go through one after another
 
@@ -25,9 +25,11 @@ __global__ void short_conv_silu_kernel(TO* __restrict__ y, int y_stride, const T
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const int t0 = blockIdx.x * tokens_per_block;
   if (c >= C || t0 >= n_tokens) return;
-  float wk[SC_MAX_TAPS];
+  // the filter right-aligned in 8 places (the last one is the current token's), zeros before it
+  constexpr int M = SC_MAX_TAPS - 1;
+  float wr[SC_MAX_TAPS];
 #pragma unroll
-  for (int j = 0; j < SC_MAX_TAPS; ++j) wk[j] = j < K ? to_f32<T>(w[(size_t)c * K + j]) : 0.f;
+  for (int m = 0; m < SC_MAX_TAPS; ++m) wr[m] = m >= SC_MAX_TAPS - K ? to_f32<T>(w[(size_t)c * K + (m - (SC_MAX_TAPS - K))]) : 0.f;
   const float b = bias ? to_f32<T>(bias[c]) : 0.f;
   // the request of the tile's first token (binary search over the starts), then walk on
   int lo = 0, hi = n_seqs - 1;
@@ -36,23 +38,40 @@ __global__ void short_conv_silu_kernel(TO* __restrict__ y, int y_stride, const T
     if (cu_q[mid] <= t0) lo = mid; else hi = mid - 1;
   }
   int s = lo;
-  const int t_end = min(t0 + tokens_per_block, n_tokens);
-  for (int t = t0; t < t_end; ++t) {
-    while (s + 1 < n_seqs && cu_q[s + 1] <= t) ++s;
-    const int i = t - cu_q[s];                      // index within this step's portion
+  int seq_first = cu_q[s], next_first = cu_q[s + 1];
+  float win[M];                                     // the inputs before the current token, the latest last
+  // the window in front of token t of request s: earlier tokens of this portion, behind them the request's state
+  auto fill = [&](int t) {
+    const int i = t - seq_first;
     const int slot = slots[s];
     const bool has_past = slot >= 0 && q_start[s] > 0;
-    float acc = b;
 #pragma unroll
-    for (int j = 0; j < SC_MAX_TAPS; ++j) {
-      if (j < K) {
-        const int rel = i - (K - 1) + j;            // input index relative to the portion's first token
-        float v = 0.f;
-        if (rel >= 0) v = to_f32<T>(x[(size_t)(t - (K - 1) + j) * x_stride + c]);
+    for (int m = 0; m < M; ++m) {
+      float v = 0.f;
+      if (m >= M - (K - 1)) {
+        const int rel = i - M + m;                  // index in the portion; negative: before it
+        if (rel >= 0) v = to_f32<T>(x[(size_t)(t - M + m) * x_stride + c]);
         else if (has_past) v = state[(size_t)slot * state_stride + (size_t)(K - 1 + rel) * C + c];
-        acc = fmaf(wk[j], v, acc);
       }
+      win[m] = v;
     }
+  };
+  fill(t0);
+  const int t_end = min(t0 + tokens_per_block, n_tokens);
+  for (int t = t0; t < t_end; ++t) {
+    if (t >= next_first) {                          // the next request begins (requests without tokens are passed over)
+      while (s + 1 < n_seqs && cu_q[s + 1] <= t) ++s;
+      seq_first = cu_q[s];
+      next_first = cu_q[s + 1];
+      fill(t);
+    }
+    const float xt = to_f32<T>(x[(size_t)t * x_stride + c]);
+    float acc = fmaf(wr[M], xt, b);
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc = fmaf(wr[m], win[m], acc);
+#pragma unroll
+    for (int m = 0; m + 1 < M; ++m) win[m] = win[m + 1];
+    win[M - 1] = xt;
     y[(size_t)t * y_stride + c] = from_f32<TO>(acc / (1.0f + expf(-acc)));
   }
 }

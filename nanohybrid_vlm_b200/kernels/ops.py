@@ -246,12 +246,15 @@ def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int
          n_seqs, n_tokens, nq, nkv, dk, dv, row, page_size, n_pages, int(window), float(scale), _ptr(sinks), stream_ptr())
 
 
+SINK_ATTENTION_ON_TENSOR_CORES = True     # tests switch it off to compare with the CUDA-core kernel at the same shapes
+
+
 def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, dv: int, scale: float, sinks=None,
                    window: int = 0) -> None:
     """Attention of the step's tokens over the cache for layers with a sink and / or value heads of another size
     than their key heads: picks the kernel for the dtype and sizes.  bfloat16 with key and value heads of one size
     (in steps of 16) runs on the tensor cores like ``attention``; float32 and unequal head sizes on the CUDA cores."""
-    if (q.dtype == torch.bfloat16 and dk == dv and kv_pages.shape[-1] == dk
+    if (SINK_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16 and dk == dv and kv_pages.shape[-1] == dk
             and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
         attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
                               batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
