@@ -158,6 +158,7 @@ def short_conv_silu(out, x, weight, bias, state, batch) -> None:
          batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
 
 
+SCAN_GROUP4 = -1    # the delta rule's scan four tokens per round of its chain: -1 is the kernel's choice (off); tests set 1
 SCAN_LANES = 0      # lanes per state column in the recurrent scans: 0 is the kernels' own choice; tests set 4, 8, 16, 32
 
 
@@ -170,15 +171,17 @@ def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int,
     assert qkv.stride(1) == 1 and qkv.shape[1] == 2 * G * d + H * dv
     assert o.dtype == ba.dtype == a_log.dtype == dt_bias.dtype == state.dtype == torch.float32
     assert o.is_contiguous() and o.shape == (T, H * dv) and ba.is_contiguous() and ba.shape == (T, 2 * H)
-    scratch = torch.empty(T * (2 * G * d + G + H * dv + 2 * H), dtype=torch.float32, device=qkv.device)
+    scratch = torch.empty(T * (2 * G * d + 9 * G + H * dv + 2 * H), dtype=torch.float32, device=qkv.device)
     at, ptrs = 0, []
-    for n in (T * G * d, T * G * d, T * H * dv, T * G, T * H, T * H):     # qn, kn, v32 (16-byte aligned for d, dv in steps of 4), kq, beta, decay
+    # qn, kn, v32, pairs (16-byte aligned for d, dv in steps of 4), then kq, beta, decay
+    for n in (T * G * d, T * G * d, T * H * dv, T * G * 8, T * G, T * H, T * H):
         ptrs.append(scratch.data_ptr() + 4 * at)
         at += n
-    qn, kn, v32, kq, beta, decay = ptrs
+    qn, kn, v32, pairs, kq, beta, decay = ptrs
     call("nhv_delta_rule", dtype_code(qkv), o.data_ptr(), qkv.data_ptr(), qkv.stride(0), ba.data_ptr(), a_log.data_ptr(),
          dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qn, kn, kq, v32, beta, decay, batch.cu_q.data_ptr(),
-         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, SCAN_LANES, stream_ptr())
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, SCAN_LANES, SCAN_GROUP4, pairs,
+         stream_ptr())
 
 
 def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: int, N: int, G: int) -> None:

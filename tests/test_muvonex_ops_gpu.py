@@ -108,12 +108,13 @@ def plain_delta(qkv, ba, a_log, dt_bias, G, H, d, dv):
     return pm.delta_recurrence(q, k, v, beta, decay).reshape(T, H * dv)
 
 
-@pytest.fixture(params=[0, 4, 8, 16, 32])
+@pytest.fixture(params=[(0, -1), (4, 0), (8, 0), (16, 0), (32, 0), (0, 1)], ids=lambda p: f"lanes{p[0]}_group{p[1]}")
 def lanes(request, ops):
-    """Every way of laying a state column over lanes (0: chosen by the size of the step)."""
-    ops.SCAN_LANES = request.param
+    """Every form of the scans: a state column over 4 to 32 lanes (0: the kernel's choice), the delta rule one token
+    or four tokens per round of its chain (-1: chosen by the size of the step)."""
+    ops.SCAN_LANES, ops.SCAN_GROUP4 = request.param
     yield request.param
-    ops.SCAN_LANES = 0
+    ops.SCAN_LANES, ops.SCAN_GROUP4 = 0, -1
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
