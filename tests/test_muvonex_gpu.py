@@ -48,7 +48,14 @@ MUV_B = dict(
             dict(heads=6, groups=3, state=24, vdim=20, conv=4, norm_groups=1), 1.0, 1.0)),
         dict(type="delta", mlp=dict(kind="dense", ff=64), mixer=delta(5, 1, 32, 40, 1)),
     ])
-MODELS = {"A": (MUV_A, 11), "B": (MUV_B, 12)}
+# no attention anywhere: nothing is kept in pages, only state slots; sizes that are no multiple of 4
+MUV_C = dict(
+    architecture="Muvonex", vocab=97, width=72, embedding=dict(scale=1.0), norm=dict(eps=1e-6), residual_mult=0.7,
+    layers=[
+        dict(type="delta", mlp=dict(kind="dense", ff=90), mixer=delta(2, 2, 34, 38, 3)),
+        dict(type="delta", mlp=None, mixer=delta(6, 3, 32, 48, 8)),
+    ])
+MODELS = {"A": (MUV_A, 11), "B": (MUV_B, 12), "C": (MUV_C, 13)}
 LENGTHS = (70, 41, 97, 2, 33, 129, 1, 9, 55)
 # the root mean square over the vocabulary of a position's error (its mean taken off: a shift of all logits changes
 # no probability), as a share of the spread of the logits
@@ -119,7 +126,7 @@ def test_replay_matches_plain(name, mode, dtype, models, references, tmp_path):
     check(got, references[name], reqs, dtype)
 
 
-@pytest.mark.parametrize("name", list(MODELS))
+@pytest.mark.parametrize("name", ["A", "B"])
 def test_float32_logits_do_not_depend_on_the_cutting(name, models, tmp_path):
     """Every kernel fixes the order of its sums per output, so in float32 a position's logits are the same bits
     however its tokens were cut and batched, and wherever its pages and its state slot lie."""
@@ -153,13 +160,14 @@ def plain_greedy(cfg, w, prompt, n):
     return toks[len(prompt):]
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
 @pytest.mark.parametrize("eager", [True, False])
-def test_greedy_generation_through_the_engine(eager, models):
+def test_greedy_generation_through_the_engine(eager, name, models):
     """``LLM.generate`` with more prompts than state slots and a token budget that cuts prompts into portions: the
     scheduler admits, batches, frees and reuses slots; tokens equal the plain model's greedy choice.  With captured
     decode steps (eager False) the batch is padded with idle entries that hold no slot."""
     from nanohybrid_vlm_b200 import LLM, SamplingParams
-    folder, cfg, w = models["B"]
+    folder, cfg, w = models[name]
     rng = np.random.default_rng(9)
     prompts = [rng.integers(0, cfg["vocab"], n).tolist() for n in (23, 5, 41, 1, 12)]
     llm = LLM(folder, dtype="float32", kvcache_block_size=8, num_kvcache_blocks=40, max_num_batched_tokens=16,
