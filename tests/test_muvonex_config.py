@@ -93,3 +93,15 @@ def test_plain_model_carries_its_states():
     a, S = pm.delta_recurrence(q[:5], k[:5], v[:5], beta[:5], decay[:5], torch.zeros(H, d, dv, dtype=torch.float64))
     b, _ = pm.delta_recurrence(q[5:], k[5:], v[5:], beta[5:], decay[5:], S)
     torch.testing.assert_close(torch.cat([a, b]), whole)
+
+
+def test_random_weights_folder(tmp_path):
+    """The random-weights mode writes every tensor the design names, under its checkpoint name and shape, and the
+    plain model runs on the folder."""
+    from safetensors.torch import load_file
+    from nanohybrid_vlm_b200.weights import write_random_model
+    write_random_model(str(tmp_path), dict(CFG, dtype="bfloat16"), seed=3)
+    tensors = load_file(str(tmp_path / "model.safetensors"))
+    assert {k: tuple(v.shape) for k, v in tensors.items()} == pm.tensor_shapes(CFG)
+    logits = pm.forward(CFG, {k: v.to(torch.float64) for k, v in tensors.items()}, [1, 2, 3, 4])
+    assert logits.shape == (4, CFG["vocab"]) and torch.isfinite(logits).all()

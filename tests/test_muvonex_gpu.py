@@ -175,3 +175,22 @@ def test_greedy_generation_through_the_engine(eager, name, models):
     out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True), use_tqdm=False)
     for p, o in zip(prompts, out):
         assert o["token_ids"] == plain_greedy(cfg, w, p, 7)
+
+
+def test_command_line_generates_the_plain_models_tokens(models):
+    """``python -m nanohybrid_vlm_b200.cli generate`` on a Muvonex folder: the registry picks the model by config.json."""
+    import subprocess
+    import sys
+    folder, cfg, w = models["A"]
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, cfg["vocab"], n).tolist() for n in (6, 19)]
+    args = [sys.executable, "-m", "nanohybrid_vlm_b200.cli", "generate", "--model", folder, "--dtype", "float32",
+            "--temperature", "0", "--max-tokens", "5", "--ignore-eos", "--kvcache-block-size", "16", "--num-kvcache-blocks",
+            "16", "--max-num-seqs", "2", "--max-model-len", "64", "--max-num-batched-tokens", "32", "--quiet"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    env = dict(os.environ, PYTHONPATH=tt.ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run(args, capture_output=True, text=True, env=env, cwd=tt.ROOT)
+    assert r.returncode == 0, r.stderr[-3000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [l["token_ids"] for l in lines] == [plain_greedy(cfg, w, p, 5) for p in prompts]
