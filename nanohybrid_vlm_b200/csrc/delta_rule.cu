@@ -493,6 +493,159 @@ __global__ void __launch_bounds__(DF_THREADS) delta_scan_block4_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------- several columns per lane
+// The same scan, token by token in the same order per column (the same bits), with CPT columns of the state in
+// each lane: a lane's rows of k and q, read once from shared memory, serve all its columns, and the columns' chains
+// run side by side in one warp.  A block holds 16 * CPT columns (column c of a lane is 16 * c to the right).
+template <int R, int CPT>
+__global__ void __launch_bounds__(DF_THREADS) delta_scan_wide_kernel(
+    float* __restrict__ o_out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ kq,
+    const float* __restrict__ v32, int v_stride, const float* __restrict__ beta, const float* __restrict__ decay,
+    float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int G, int H, int d, int dv) {
+  constexpr int LANES = 8, NTC = DF_THREADS / LANES, COLS = NTC * CPT;
+  extern __shared__ __align__(16) float smem[];
+  pdl_wait();
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
+  const int g = h / (H / G);
+  const int first = cu_q[s], n = cu_q[s + 1] - first;
+  const int slot = slots[s];
+  const int tid = threadIdx.x;
+  const int ncol = min(COLS, dv - col0);               // a multiple of 4
+  if (slot < 0) {
+    for (int i = tid; i < n * ncol; i += DF_THREADS)
+      o_out[((size_t)(first + i / ncol) * H + h) * dv + col0 + i % ncol] = 0.f;
+    return;
+  }
+  constexpr int DP = R * LANES;
+  constexpr int stage_floats = DF_CHUNK * (2 * DP + COLS + 4);
+  if (d < DP)
+    for (int i = tid; i < 2 * 2 * DF_CHUNK * (DP - d); i += DF_THREADS) {
+      const int row = i / (DP - d), c = i - row * (DP - d);
+      smem[(row / (2 * DF_CHUNK)) * stage_floats + (row % (2 * DF_CHUNK)) * DP + d + c] = 0.f;
+    }
+  const int cl = tid / LANES, part = tid % LANES;
+  bool live[CPT];
+  float* st[CPT];
+  f32x2 S[CPT][R / 2];
+  const bool fresh = q_start[s] == 0;
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) {
+    live[c] = cl + NTC * c < ncol;
+    st[c] = state + (size_t)slot * state_stride + ((size_t)h * dv + col0 + (live[c] ? cl + NTC * c : 0)) * d;
+#pragma unroll
+    for (int j = 0; j < R / 4; ++j) {
+      const int i = 4 * (part + LANES * j);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live[c] && !fresh && i < d) v = make_float4(st[c][i], st[c][i + 1], st[c][i + 2], st[c][i + 3]);
+      S[c][2 * j] = f2_pack(v.x, v.y);
+      S[c][2 * j + 1] = f2_pack(v.z, v.w);
+    }
+  }
+
+  auto fetch = [&](int c0, int stage) {
+    float* qs = smem + stage * stage_floats;           // [CHUNK][DP]
+    float* ks = qs + DF_CHUNK * DP;                    // [CHUNK][DP]
+    float* vs = ks + DF_CHUNK * DP;                    // [CHUNK][COLS]
+    float* sc = vs + DF_CHUNK * COLS;                  // [CHUNK][4]: decay, beta, k . q
+    const int cn = min(DF_CHUNK, n - c0);
+    const int d4 = d >> 2, c4 = ncol >> 2;
+    for (int i = tid; i < cn * d4; i += DF_THREADS) {
+      const int tt = i / d4, c = i - tt * d4;
+      const size_t row = ((size_t)(first + c0 + tt) * G + g) * d + 4 * c;
+      cp_async16(qs + tt * DP + 4 * c, qn + row);
+      cp_async16(ks + tt * DP + 4 * c, kn + row);
+    }
+    for (int i = tid; i < cn * c4; i += DF_THREADS) {
+      const int tt = i / c4, c = i - tt * c4;
+      cp_async16(vs + tt * COLS + 4 * c, v32 + (size_t)(first + c0 + tt) * v_stride + h * dv + col0 + 4 * c);
+    }
+    for (int i = tid; i < cn * 3; i += DF_THREADS) {
+      const int tt = i / 3, w = i - tt * 3;
+      const size_t tok = first + c0 + tt;
+      cp_async4(sc + tt * 4 + w, w == 0 ? decay + tok * H + h : (w == 1 ? beta + tok * H + h : kq + tok * G + g));
+    }
+  };
+
+  const int n_chunks = (n + DF_CHUNK - 1) / DF_CHUNK;
+  if (n_chunks > 0) fetch(0, 0);
+  cp_async_commit();
+  for (int ci = 0; ci < n_chunks; ++ci) {
+    const int c0 = ci * DF_CHUNK, stage = ci & 1;
+    if (ci + 1 < n_chunks) fetch(c0 + DF_CHUNK, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const float* qs = smem + stage * stage_floats + 4 * part;
+    const float* ks = qs + DF_CHUNK * DP;
+    const float* vs = smem + stage * stage_floats + 2 * DF_CHUNK * DP;
+    const float* sc = vs + DF_CHUNK * COLS;
+    const int cn = min(DF_CHUNK, n - c0);
+    for (int tt = 0; tt < cn; ++tt) {
+      const float4 scv = *reinterpret_cast<const float4*>(sc + tt * 4);
+      const float gt = scv.x, bt = scv.y, kqt = scv.z;
+      ulonglong2 kk[R / 4], qq[R / 4];
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        kk[j] = *reinterpret_cast<const ulonglong2*>(ks + tt * DP + 4 * LANES * j);
+        qq[j] = *reinterpret_cast<const ulonglong2*>(qs + tt * DP + 4 * LANES * j);
+      }
+      float sk[CPT], sq[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        f32x2 ak[2] = {0ull, 0ull}, aq[2] = {0ull, 0ull};
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          ak[0] = f2_fma(S[c][2 * j], kk[j].x, ak[0]);     aq[0] = f2_fma(S[c][2 * j], qq[j].x, aq[0]);
+          ak[1] = f2_fma(S[c][2 * j + 1], kk[j].y, ak[1]); aq[1] = f2_fma(S[c][2 * j + 1], qq[j].y, aq[1]);
+        }
+        sk[c] = f2_sum(ak[0], ak[1]);
+        sq[c] = f2_sum(aq[0], aq[1]);
+      }
+      const bool odd = part & 1;
+      float mine[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) mine[c] = (odd ? sq[c] : sk[c]) + __shfl_xor_sync(0xffffffffu, odd ? sk[c] : sq[c], 1);
+#pragma unroll
+      for (int off = 2; off < LANES; off <<= 1)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) mine[c] += __shfl_xor_sync(0xffffffffu, mine[c], off);
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const float theirs = __shfl_xor_sync(0xffffffffu, mine[c], 1);
+        const float skc = odd ? theirs : mine[c], sqc = odd ? mine[c] : theirs;
+        const float u = bt * ((live[c] ? vs[tt * COLS + cl + NTC * c] : 0.f) - gt * skc);
+        const f32x2 uu = f2_pack(u, u), gg = f2_pack(gt, gt);
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          S[c][2 * j] = f2_fma(kk[j].x, uu, f2_mul(S[c][2 * j], gg));
+          S[c][2 * j + 1] = f2_fma(kk[j].y, uu, f2_mul(S[c][2 * j + 1], gg));
+        }
+        if (live[c] && part == 0)
+          o_out[((size_t)(first + c0 + tt) * H + h) * dv + col0 + cl + NTC * c] = fmaf(u, kqt, gt * sqc);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  pdl_launch_dependents();
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
+    if (live[c]) {
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const int i = 4 * (part + LANES * j);
+        if (i < d) {
+          float4 v;
+          f2_unpack(S[c][2 * j], v.x, v.y);
+          f2_unpack(S[c][2 * j + 1], v.z, v.w);
+          st[c][i] = v.x; st[c][i + 1] = v.y; st[c][i + 2] = v.z; st[c][i + 3] = v.w;
+        }
+      }
+    }
+}
+
 template <typename T, int R>
 __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_scan_kernel(
     float* __restrict__ o_out, const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
@@ -586,14 +739,15 @@ __global__ void __launch_bounds__(DR_COLS * DR_PARTS) delta_scan_kernel(
 
 // o_out [T, H, dv] fp32.  lanes: 4, 8, 16 or 32 lanes per column of the state, or 0 for the kernel's own choice.
 // group4: 1 takes four tokens per round of the chain (needs pairs [T, G, 8] as scratch), 0 one, -1 chooses by the
-// size of the step.
+// size of the step.  cpt: 2 or 4 columns of the state per lane (8 lanes a column, d up to 128), 1 one, 0 the
+// kernel's choice.
 // Scratch given by the caller, all fp32: qn, kn [T, G, d]; kq [T, G]; v32 [T, H, dv]; beta,
 // decay [T, H].
 NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_stride, const float* ba,
                            const float* a_log, const float* dt_bias, float* state, long state_stride, float* qn,
                            float* kn, float* kq, float* v32, float* beta, float* decay, const int* cu_q,
                            const int* q_start, const int* slots, int n_seqs, int n_tokens, int G, int H, int d, int dv,
-                           int lanes, int group4, float* pairs, cudaStream_t stream) {
+                           int lanes, int group4, float* pairs, int cpt, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(G > 0 && H > 0 && H % G == 0, "delta_rule: %d heads do not divide into %d q/k heads", H, G);
   NHV_REQUIRE(d > 0 && d <= 256 && dv > 0, "delta_rule: a q/k head of %d is beyond the supported 256", d);
@@ -641,6 +795,35 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
     else if (need <= 16) BLOCK4(16);
     else BLOCK4(32);
 #undef BLOCK4
+  } else if (fast && cpt > 1 && d <= 128) {
+    if (cpt != 2) cpt = 4;
+    const int cols = 16 * cpt;
+    dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
+    const int need = (d + 7) / 8;
+#define WIDE(R, C)                                                                                                   \
+  do {                                                                                                               \
+    static bool attr = false;                                                                                        \
+    if (!attr) {                                                                                                     \
+      NHV_CUDA(cudaFuncSetAttribute(delta_scan_wide_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                    232448), "delta_rule");                                                          \
+      attr = true;                                                                                                   \
+    }                                                                                                                \
+    nhv_launch(delta_scan_wide_kernel<R, C>, grid, DF_THREADS,                                                       \
+               nhv_spread_smem((size_t)2 * DF_CHUNK * (2 * R * 8 + 16 * C + 4) * sizeof(float),                      \
+                               (long)grid.x * grid.y * grid.z), stream,                                             \
+               o_out, (const float*)qn, (const float*)kn, (const float*)kq, v_src, v_stride, (const float*)beta,    \
+               (const float*)decay, state, state_stride, cu_q, q_start, slots, G, H, d, dv);                        \
+  } while (0)
+#define WIDE_C(C)                          \
+  do {                                     \
+    if (need <= 4) WIDE(4, C);             \
+    else if (need <= 8) WIDE(8, C);        \
+    else WIDE(16, C);                      \
+  } while (0)
+    if (cpt == 2) WIDE_C(2);
+    else WIDE_C(4);
+#undef WIDE_C
+#undef WIDE
   } else if (fast) {
     // lanes per column: 8 measured fastest for one long request (244 ns a token against 254 with 16 lanes and 299
     // with 32: the shuffle rounds of the sum over lanes are the longest stretch of a token's chain) and for full

@@ -158,6 +158,7 @@ def short_conv_silu(out, x, weight, bias, state, batch) -> None:
          batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
 
 
+SCAN_COLUMNS = 0    # columns of the delta rule's state per lane: 0 is the kernel's choice; tests set 1, 2, 4
 SCAN_GROUP4 = -1    # the delta rule's scan four tokens per round of its chain: -1 is the kernel's choice (off); tests set 1
 SCAN_LANES = 0      # lanes per state column in the recurrent scans: 0 is the kernels' own choice; tests set 4, 8, 16, 32
 
@@ -181,7 +182,7 @@ def delta_rule(o, qkv, ba, a_log, dt_bias, state, batch, G: int, H: int, d: int,
     call("nhv_delta_rule", dtype_code(qkv), o.data_ptr(), qkv.data_ptr(), qkv.stride(0), ba.data_ptr(), a_log.data_ptr(),
          dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qn, kn, kq, v32, beta, decay, batch.cu_q.data_ptr(),
          batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, G, H, d, dv, SCAN_LANES, SCAN_GROUP4, pairs,
-         stream_ptr())
+         SCAN_COLUMNS, stream_ptr())
 
 
 def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: int, N: int, G: int) -> None:

@@ -108,13 +108,14 @@ def plain_delta(qkv, ba, a_log, dt_bias, G, H, d, dv):
     return pm.delta_recurrence(q, k, v, beta, decay).reshape(T, H * dv)
 
 
-@pytest.fixture(params=[(0, -1), (4, 0), (8, 0), (16, 0), (32, 0), (0, 1)], ids=lambda p: f"lanes{p[0]}_group{p[1]}")
+@pytest.fixture(params=[(0, -1, 0), (4, 0, 1), (8, 0, 1), (16, 0, 1), (32, 0, 1), (0, 1, 1), (0, 0, 2), (0, 0, 4)],
+                ids=lambda p: f"lanes{p[0]}_group{p[1]}_columns{p[2]}")
 def lanes(request, ops):
     """Every form of the scans: a state column over 4 to 32 lanes (0: the kernel's choice), the delta rule one token
-    or four tokens per round of its chain (-1: chosen by the size of the step)."""
-    ops.SCAN_LANES, ops.SCAN_GROUP4 = request.param
+    or four tokens per round of its chain (-1: the kernel's choice), one, two or four columns per lane."""
+    ops.SCAN_LANES, ops.SCAN_GROUP4, ops.SCAN_COLUMNS = request.param
     yield request.param
-    ops.SCAN_LANES, ops.SCAN_GROUP4 = 0, -1
+    ops.SCAN_LANES, ops.SCAN_GROUP4, ops.SCAN_COLUMNS = 0, -1, 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
