@@ -770,6 +770,13 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
   // four tokens per round of the chain: 225 against 252 ns a token for one 4,096-token request (16 heads, d = dv =
   // 128), the same at 4 or more requests.  Too little to give up sums in one fixed order for: off unless asked for.
   if (group4 < 0) group4 = 0;
+  // columns per lane: one while the blocks of 16 columns leave SMs idle (one or two long requests: 259 ns a token
+  // against 265 and 347 with 2 and 4 columns), more when the SMs are full and reads of k and q from shared memory
+  // are what costs (8 requests of 512 tokens: 878, 673, 604 ns per token-step; 64 single tokens: 36, 32, 31 µs)
+  if (cpt <= 0) {
+    const long blocks16 = (long)n_seqs * H * ((dv + 15) / 16);
+    cpt = blocks16 <= 2 * 148 ? 1 : (blocks16 <= 6 * 148 ? 2 : 4);
+  }
   if (fast && group4 && pairs) {
     const long items = (long)n_tokens * G;
     nhv_launch(delta_pairs_kernel, (int)((items + 7) / 8), 256, 0, stream, pairs, (const float*)qn, (const float*)kn,
@@ -795,7 +802,7 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
     else if (need <= 16) BLOCK4(16);
     else BLOCK4(32);
 #undef BLOCK4
-  } else if (fast && cpt > 1 && d <= 128) {
+  } else if (fast && cpt > 1 && d <= 128 && (lanes == 0 || lanes == 8)) {
     if (cpt != 2) cpt = 4;
     const int cols = 16 * cpt;
     dim3 grid(n_seqs, H, (dv + cols - 1) / cols);

@@ -254,17 +254,202 @@ __global__ void __launch_bounds__(SF_THREADS) ssd_scan_fast_kernel(
   }
 }
 
+// The same scan with CPT columns of the state in each lane (8 lanes a column): a lane's rows of B and C, read once
+// from shared memory, serve all its columns.  A block holds 16 * CPT columns (column c of a lane is 16 * c to the
+// right).  Every column sees its tokens in the same order as above: the same bits.
+template <int R, int CPT>
+__global__ void __launch_bounds__(SF_THREADS) ssd_scan_wide_kernel(
+    float* __restrict__ y, const float* __restrict__ xbc, int xbc_stride, const float* __restrict__ dt_raw, int dt_stride,
+    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+    float* __restrict__ state, long state_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start,
+    const int* __restrict__ slots, int H, int P, int N, int G) {
+  constexpr int LANES = 8, NTC = SF_THREADS / LANES, COLS = NTC * CPT;
+  extern __shared__ __align__(16) float smem[];
+  pdl_wait();
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
+  const int gr = h / (H / G);
+  const int inner = H * P;
+  const int first = cu_q[s], n = cu_q[s + 1] - first;
+  const int slot = slots[s];
+  const int tid = threadIdx.x;
+  const int ncol = min(COLS, P - col0);                // a multiple of 4
+  if (slot < 0) {
+    for (int i = tid; i < n * ncol; i += SF_THREADS) y[(size_t)(first + i / ncol) * inner + h * P + col0 + i % ncol] = 0.f;
+    return;
+  }
+  constexpr int NP = R * LANES;
+  constexpr int stage_floats = SF_CHUNK * (2 * NP + COLS + 2);
+  if (N < NP)
+    for (int i = tid; i < 2 * 2 * SF_CHUNK * (NP - N); i += SF_THREADS) {
+      const int row = i / (NP - N), c = i - row * (NP - N);
+      smem[(row / (2 * SF_CHUNK)) * stage_floats + (row % (2 * SF_CHUNK)) * NP + N + c] = 0.f;
+    }
+  const int cl = tid / LANES, part = tid % LANES;
+  const float rate = expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
+  bool live[CPT];
+  float* st[CPT];
+  f32x2 S[CPT][R / 2];
+  const bool fresh = q_start[s] == 0;
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) {
+    live[c] = cl + NTC * c < ncol;
+    st[c] = state + (size_t)slot * state_stride + ((size_t)h * P + col0 + (live[c] ? cl + NTC * c : 0)) * N;
+#pragma unroll
+    for (int j = 0; j < R / 4; ++j) {
+      const int i = 4 * (part + LANES * j);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live[c] && !fresh && i < N) v = make_float4(st[c][i], st[c][i + 1], st[c][i + 2], st[c][i + 3]);
+      S[c][2 * j] = f2_pack(v.x, v.y);
+      S[c][2 * j + 1] = f2_pack(v.z, v.w);
+    }
+  }
+
+  auto fetch = [&](int c0, int stage) {
+    float* Bs = smem + stage * stage_floats;           // [CHUNK][NP]
+    float* Cs = Bs + SF_CHUNK * NP;                    // [CHUNK][NP]
+    float* xs = Cs + SF_CHUNK * NP;                    // [CHUNK][COLS]
+    const int cn = min(SF_CHUNK, n - c0);
+    const int n4 = N >> 2, c4 = ncol >> 2;
+    for (int i = tid; i < cn * n4; i += SF_THREADS) {
+      const int tt = i / n4, c = i - tt * n4;
+      const float* row = xbc + (size_t)(first + c0 + tt) * xbc_stride + inner + gr * N + 4 * c;
+      ss_cp_async16(Bs + tt * NP + 4 * c, row);
+      ss_cp_async16(Cs + tt * NP + 4 * c, row + (size_t)G * N);
+    }
+    for (int i = tid; i < cn * c4; i += SF_THREADS) {
+      const int tt = i / c4, c = i - tt * c4;
+      ss_cp_async16(xs + tt * COLS + 4 * c, xbc + (size_t)(first + c0 + tt) * xbc_stride + h * P + col0 + 4 * c);
+    }
+  };
+
+  const int n_chunks = (n + SF_CHUNK - 1) / SF_CHUNK;
+  float dt_next = 0.f;
+  if (n_chunks > 0) {
+    fetch(0, 0);
+    if (tid < min(SF_CHUNK, n)) dt_next = dt_raw[(size_t)(first + tid) * dt_stride + h];
+  }
+  ss_cp_async_commit();
+  for (int ci = 0; ci < n_chunks; ++ci) {
+    const int c0 = ci * SF_CHUNK, stage = ci & 1;
+    const int cn = min(SF_CHUNK, n - c0);
+    if (ci + 1 < n_chunks) fetch(c0 + SF_CHUNK, stage ^ 1);
+    ss_cp_async_commit();
+    float* ds = smem + stage * stage_floats + SF_CHUNK * (2 * NP + COLS);      // [CHUNK][2]: decay, dt
+    if (tid < cn) {
+      const float dt = ss_softplus(dt_next + bias);
+      ds[2 * tid] = expf(-rate * dt);
+      ds[2 * tid + 1] = dt;
+    }
+    ss_cp_async_wait<1>();
+    __syncthreads();
+    if (ci + 1 < n_chunks && tid < min(SF_CHUNK, n - c0 - SF_CHUNK))
+      dt_next = dt_raw[(size_t)(first + c0 + SF_CHUNK + tid) * dt_stride + h];
+    const float* Bs = smem + stage * stage_floats + 4 * part;
+    const float* Cs = Bs + SF_CHUNK * NP;
+    const float* xs = smem + stage * stage_floats + 2 * SF_CHUNK * NP;
+    for (int tt = 0; tt < cn; ++tt) {
+      const float a = ds[2 * tt], dt = ds[2 * tt + 1];
+      const f32x2 aa = f2_pack(a, a);
+      ulonglong2 bb[R / 4], cc[R / 4];
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        bb[j] = *reinterpret_cast<const ulonglong2*>(Bs + tt * NP + 4 * LANES * j);
+        cc[j] = *reinterpret_cast<const ulonglong2*>(Cs + tt * NP + 4 * LANES * j);
+      }
+      float sum[CPT], xv[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        xv[c] = live[c] ? xs[tt * COLS + cl + NTC * c] : 0.f;
+        const float dx = dt * xv[c];
+        const f32x2 dd = f2_pack(dx, dx);
+        f32x2 acc[2] = {0ull, 0ull};
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          S[c][2 * j] = f2_fma(aa, S[c][2 * j], f2_mul(dd, bb[j].x));         acc[0] = f2_fma(S[c][2 * j], cc[j].x, acc[0]);
+          S[c][2 * j + 1] = f2_fma(aa, S[c][2 * j + 1], f2_mul(dd, bb[j].y)); acc[1] = f2_fma(S[c][2 * j + 1], cc[j].y, acc[1]);
+        }
+        sum[c] = f2_sum(acc[0], acc[1]);
+      }
+#pragma unroll
+      for (int off = 1; off < LANES; off <<= 1)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) sum[c] += __shfl_xor_sync(0xffffffffu, sum[c], off);
+#pragma unroll
+      for (int c = 0; c < CPT; ++c)
+        if (live[c] && part == 0)
+          y[(size_t)(first + c0 + tt) * inner + h * P + col0 + cl + NTC * c] = fmaf(skip, xv[c], sum[c]);
+    }
+    __syncthreads();
+  }
+  ss_cp_async_wait<0>();
+  pdl_launch_dependents();
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
+    if (live[c]) {
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const int i = 4 * (part + LANES * j);
+        if (i < N) {
+          float4 v;
+          f2_unpack(S[c][2 * j], v.x, v.y);
+          f2_unpack(S[c][2 * j + 1], v.z, v.w);
+          st[c][i] = v.x; st[c][i + 1] = v.y; st[c][i + 2] = v.z; st[c][i + 3] = v.w;
+        }
+      }
+    }
+}
+
+
 // xbc [T, H*P + 2*G*N] (x, then B, then C), dt_raw [T, >= H] fp32, y [T, H*P] fp32.  lanes: 8, 16 or 32 lanes per
 // column of the state in the fast form, or 0 to choose by the size of the step.
 NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, const float* dt_raw, int dt_stride,
                          const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                          long state_stride, const int* cu_q, const int* q_start, const int* slots, int n_seqs,
-                         int n_tokens, int H, int P, int N, int G, int lanes, cudaStream_t stream) {
+                         int n_tokens, int H, int P, int N, int G, int lanes, int cpt, cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(G > 0 && H > 0 && H % G == 0, "ssd_scan: %d heads do not divide into %d groups", H, G);
   NHV_REQUIRE(N > 0 && N <= 256 && P > 0, "ssd_scan: a state of %d rows is beyond the supported 256", N);
   NHV_REQUIRE(state_stride >= (long)H * P * N, "ssd_scan: the state holds fewer than heads * P * N floats");
-  if (dtype == NHV_F32 && N % 4 == 0 && P % 4 == 0 && xbc_stride % 4 == 0 && ((uintptr_t)xbc % 16) == 0) {
+  const bool fast = dtype == NHV_F32 && N % 4 == 0 && P % 4 == 0 && xbc_stride % 4 == 0 && ((uintptr_t)xbc % 16) == 0;
+  // columns per lane (cpt: 1, 2, 4, or 0 to choose): one while the blocks of 16 columns leave SMs idle, more when
+  // the SMs are full and the reads of B and C from shared memory are what costs
+  if (cpt <= 0) {
+    const long blocks16 = (long)n_seqs * H * ((P + 15) / 16);
+    cpt = blocks16 <= 2 * 148 ? 1 : (blocks16 <= 6 * 148 ? 2 : 4);
+  }
+  if (fast && cpt > 1 && N <= 128 && lanes != 4 && lanes != 16 && lanes != 32) {
+    if (cpt != 2) cpt = 4;
+    const int cols = 16 * cpt;
+    dim3 wgrid(n_seqs, H, (P + cols - 1) / cols);
+    const int need = (N + 7) / 8;
+#define WIDE(R, C)                                                                                                   \
+  do {                                                                                                               \
+    static bool attr = false;                                                                                        \
+    if (!attr) {                                                                                                     \
+      NHV_CUDA(cudaFuncSetAttribute(ssd_scan_wide_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                    232448), "ssd_scan");                                                            \
+      attr = true;                                                                                                   \
+    }                                                                                                                \
+    nhv_launch(ssd_scan_wide_kernel<R, C>, wgrid, SF_THREADS,                                                        \
+               nhv_spread_smem((size_t)2 * SF_CHUNK * (2 * R * 8 + 16 * C + 2) * sizeof(float),                      \
+                               (long)wgrid.x * wgrid.y * wgrid.z), stream,                                          \
+               y, (const float*)xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, d_skip, state, state_stride,    \
+               cu_q, q_start, slots, H, P, N, G);                                                                    \
+  } while (0)
+#define WIDE_C(C)                          \
+  do {                                     \
+    if (need <= 4) WIDE(4, C);             \
+    else if (need <= 8) WIDE(8, C);        \
+    else WIDE(16, C);                      \
+  } while (0)
+    if (cpt == 2) WIDE_C(2);
+    else WIDE_C(4);
+#undef WIDE_C
+#undef WIDE
+    NHV_CHECK_LAUNCH("ssd_scan");
+    return 0;
+  }
+  if (fast) {
     // lanes per column: 8 measured fastest for one long request (244 ns a token against 254 with 16 lanes and 299
     // with 32: the shuffle rounds of the sum over lanes are the longest stretch of a token's chain) and for full
     // batches (fewest instructions in all); 16 and 32 stay for the tests

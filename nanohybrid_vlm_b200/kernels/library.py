@@ -40,7 +40,7 @@ _SIGNATURES = {
     "nhv_scaled_sum": [I, P, P, P, F, F, c_size_t, P],
     "nhv_short_conv_silu": [I, I, P, I, P, I, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
     "nhv_delta_rule": [I, P, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P],
-    "nhv_ssd_scan": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, I, P],
+    "nhv_ssd_scan": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, I, I, P],
     "nhv_gated_rmsnorm": [I, P, I, P, P, I, P, I, I, I, I, F, I, P],
     "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],

@@ -158,7 +158,7 @@ def short_conv_silu(out, x, weight, bias, state, batch) -> None:
          batch.state_slots.data_ptr(), batch.n_seqs, x.shape[0], C, K, stream_ptr())
 
 
-SCAN_COLUMNS = 0    # columns of the delta rule's state per lane: 0 is the kernel's choice; tests set 1, 2, 4
+SCAN_COLUMNS = 0    # columns of a scan's state per lane: 0 is the kernel's choice; tests set 1, 2, 4
 SCAN_GROUP4 = -1    # the delta rule's scan four tokens per round of its chain: -1 is the kernel's choice (off); tests set 1
 SCAN_LANES = 0      # lanes per state column in the recurrent scans: 0 is the kernels' own choice; tests set 4, 8, 16, 32
 
@@ -195,7 +195,8 @@ def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: in
     assert y.is_contiguous() and y.shape == (T, H * P)
     call("nhv_ssd_scan", dtype_code(xbc), y.data_ptr(), xbc.data_ptr(), xbc.stride(0), dt_raw.data_ptr(), dt_raw.stride(0),
          dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(),
-         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, P, N, G, SCAN_LANES, stream_ptr())
+         batch.q_start.data_ptr(), batch.state_slots.data_ptr(), batch.n_seqs, T, H, P, N, G, SCAN_LANES,
+         SCAN_COLUMNS, stream_ptr())
 
 
 def gated_rmsnorm(out, y, z, weight, n_groups: int, eps: float, gate_first: bool) -> None:
