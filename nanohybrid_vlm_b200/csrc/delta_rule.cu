@@ -775,7 +775,8 @@ NHV_API int nhv_delta_rule(int dtype, float* o_out, const void* qkv, int qkv_str
   // are what costs (8 requests of 512 tokens: 878, 673, 604 ns per token-step; 64 single tokens: 36, 32, 31 µs)
   if (cpt <= 0) {
     const long blocks16 = (long)n_seqs * H * ((dv + 15) / 16);
-    cpt = blocks16 <= 2 * 148 ? 1 : (blocks16 <= 6 * 148 ? 2 : 4);
+    if (n_tokens >= 8 * (long)n_seqs) cpt = blocks16 <= 2 * 148 ? 1 : (blocks16 <= 6 * 148 ? 2 : 4);
+    else cpt = blocks16 >= 16 * 148 ? 4 : (blocks16 >= 8 * 148 ? 2 : 1);     // single tokens: the states stream in and out, and many small blocks keep more reads in flight
   }
   if (fast && group4 && pairs) {
     const long items = (long)n_tokens * G;

@@ -415,7 +415,8 @@ NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, c
   // the SMs are full and the reads of B and C from shared memory are what costs
   if (cpt <= 0) {
     const long blocks16 = (long)n_seqs * H * ((P + 15) / 16);
-    cpt = blocks16 <= 2 * 148 ? 1 : (blocks16 <= 6 * 148 ? 2 : 4);
+    if (n_tokens >= 8 * (long)n_seqs) cpt = blocks16 <= 2 * 148 ? 1 : (blocks16 <= 6 * 148 ? 2 : 4);
+    else cpt = blocks16 >= 16 * 148 ? 4 : (blocks16 >= 8 * 148 ? 2 : 1);     // single tokens: the states stream in and out, and many small blocks keep more reads in flight
   }
   if (fast && cpt > 1 && N <= 128 && lanes != 4 && lanes != 16 && lanes != 32) {
     if (cpt != 2) cpt = 4;
