@@ -13,7 +13,8 @@ projection.
 Tensors: ``qkvg`` [2 G d + 2 H dv, width] packed from the checkpoint's ``q``, ``k``, ``v``, ``g``; ``ba`` [2 H, width]
 from ``b``, ``a``; ``conv`` [2 G d + H dv, taps] from ``q.conv``, ``k.conv``, ``v.conv``; ``A_log``, ``dt_bias`` [H]
 (float32); ``norm`` [dv]; ``o`` [width, H dv].  Per request the mixer keeps the convolutions' last taps - 1 inputs and
-S, both in float32.  beta, the decay, the unit vectors, the recurrence and the output norm are 32-bit.
+S, both in float32.  The convolutions write float32, so q, k and v enter the recurrence unrounded; beta, the decay,
+the unit vectors, the recurrence and the output norm are 32-bit.
 """
 from __future__ import annotations
 

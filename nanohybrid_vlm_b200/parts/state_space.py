@@ -11,7 +11,8 @@ square in ``norm_groups`` parts, times the weight ``norm``, and the output proje
 
 Tensors: ``in`` [2 inner + 2 G N + heads, width], ``conv`` [inner + 2 G N, taps], ``conv.b``, ``dt_bias`` / ``A_log``
 / ``D`` [heads] (float32), ``norm`` [inner], ``o`` [width, inner].  Per request the mixer keeps the last taps - 1
-inputs of the convolution and S, both in float32.  dt, the decay, the recurrence and the gated norm are 32-bit.
+inputs of the convolution and S, both in float32.  The convolution writes float32, so x, B and C enter the
+recurrence unrounded; dt, the decay, the recurrence and the gated norm are 32-bit.
 """
 from __future__ import annotations
 
