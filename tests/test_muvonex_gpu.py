@@ -1,9 +1,10 @@
 """Muvonex through the engine against the plain model (float64, token by token): the same requests whole, with
 their last tokens decoded one by one, in portions down to two tokens, and mixed with other requests in a pool so
 small that pages and state slots are used again; long decoding from a single token; greedy generation through
-``LLM.generate`` and the scheduler.  Two small configurations that differ in every size, in the order of their
+``LLM.generate`` and the scheduler.  Small configurations that differ in every size, in the order of their
 layers and in every option: groups of several heads, norm groups, a layer without a feed-forward, rotation of a
-part of the head, frequency bands or none, one tap and many."""
+part of the head, frequency bands or none, one tap and many; one without attention, one whose attention has key
+and value heads of one size."""
 import json
 import os
 
@@ -55,7 +56,20 @@ MUV_C = dict(
         dict(type="delta", mlp=dict(kind="dense", ff=90), mixer=delta(2, 2, 34, 38, 3)),
         dict(type="delta", mlp=None, mixer=delta(6, 3, 32, 48, 8)),
     ])
-MODELS = {"A": (MUV_A, 11), "B": (MUV_B, 12), "C": (MUV_C, 13)}
+# key and value heads of one size, in steps of 16: in bfloat16 this attention runs on the tensor cores
+MUV_D = dict(
+    architecture="Muvonex", vocab=260, width=96, embedding=dict(scale=4.0), norm=dict(eps=1e-6), residual_mult=0.4,
+    layers=[
+        dict(type="parallel", mlp=dict(kind="dense", ff=128), mixer=parallel(
+            dict(heads=6, kv_heads=2, dim=48, vdim=48, scale=0.15, rot=dict(base=10000.0, dims=48, scaling=dict(
+                factor=2.0, low=1.0, high=2.0, original=24))),
+            dict(heads=2, groups=1, state=32, vdim=48, conv=4, norm_groups=1), 0.9, 1.2)),
+        dict(type="delta", mlp=dict(kind="dense", ff=128), mixer=delta(3, 3, 32, 32, 4)),
+        dict(type="parallel", mlp=None, mixer=parallel(
+            dict(heads=2, kv_heads=1, dim=64, vdim=64, scale=0.125, rot=dict(base=10000.0, dims=32, scaling=None)),
+            dict(heads=4, groups=2, state=16, vdim=32, conv=2, norm_groups=2), 1.0, 1.0)),
+    ])
+MODELS = {"A": (MUV_A, 11), "B": (MUV_B, 12), "C": (MUV_C, 13), "D": (MUV_D, 14)}
 LENGTHS = (70, 41, 97, 2, 33, 129, 1, 9, 55)
 # the root mean square over the vocabulary of a position's error (its mean taken off: a shift of all logits changes
 # no probability), as a share of the spread of the logits
