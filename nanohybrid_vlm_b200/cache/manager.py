@@ -3,7 +3,8 @@ fixed-size per-request state.  Pure host bookkeeping; the tensors live in
 :mod:`.storage`.
 
 Layer runs whose mixers keep keys and values are put into *groups* by what they need to
-keep: all keys (``window`` None) or the last ``window`` of them.  Each group has a pool and
+keep: all keys (``window`` None), the last ``window`` of them, or (``chunk``) the keys of the chunk of ``chunk``
+positions that the newest token lies in (chunked attention never looks behind its chunk's start).  Each group has a pool and
 block tables of its own, because a windowed group gives pages back while a request is
 still running.  One page id of a group indexes the pages of every run of that group
 (nanovllm/engine/block_manager.py:47-131 has one such pool for all layers).
@@ -32,6 +33,12 @@ from .page_pool import OutOfPages, PagePool, StateSlotAllocator
 @dataclass(frozen=True)
 class GroupSpec:
     window: int | None      # None: keep every key
+    chunk: int | None = None    # n: only keys at or after the start of the newest token's chunk of n positions are read
+
+    @property
+    def gives_back(self) -> bool:
+        """True if a running request returns pages of this group (a window or a chunk has passed them)."""
+        return self.window is not None or self.chunk is not None
 
 
 @dataclass
@@ -61,7 +68,7 @@ class CacheManager:
         if enable_prefix_cache and not self.prefix_cache_possible(self.groups, num_state_slots):
             raise ValueError("prefix reuse needs groups that keep every key and a model without per-request state")
         self.prefix_cache = enable_prefix_cache
-        self.has_windows = any(g.window is not None for g in self.groups)
+        self.has_windows = any(g.gives_back for g in self.groups)
         self._serial = 0
         # per group: hash -> page, and for every page that carries a hash: (hash, its token ids)
         self._by_hash: list[dict[int, int]] = [{} for _ in self.groups]
@@ -70,7 +77,7 @@ class CacheManager:
 
     @staticmethod
     def prefix_cache_possible(groups, num_state_slots: int) -> bool:
-        return num_state_slots == 0 and all(g.window is None for g in groups)
+        return num_state_slots == 0 and not any(g.gives_back for g in groups)
 
     # ------------------------------------------------------------------ prefix reuse
     @staticmethod
@@ -179,10 +186,11 @@ class CacheManager:
 
     def _first_needed_page(self, g: int, num_computed: int) -> int:
         """The first logical page a query at position >= num_computed can still read."""
-        w = self.groups[g].window
-        if w is None:
-            return 0
-        return max(0, num_computed - w + 1) // self.page_size
+        w, c = self.groups[g].window, self.groups[g].chunk
+        first = 0 if w is None else max(0, num_computed - w + 1)
+        if c is not None:
+            first = max(first, num_computed // c * c)       # the next query's chunk starts here
+        return first // self.page_size
 
     def pages_needed(self, req_id, num_tokens: int) -> list[int]:
         """New pages per group so that tokens [0, num_tokens) of the request are covered."""

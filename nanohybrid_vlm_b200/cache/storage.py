@@ -44,7 +44,7 @@ class CacheLayout:
             mine: list[int | None] = []
             for leaf in leaves(need):
                 if isinstance(leaf, PagedKVNeed):
-                    g = GroupSpec(leaf.window)
+                    g = GroupSpec(leaf.window, leaf.chunk)
                     if g not in groups:
                         groups.append(g)
                     mine.append(groups.index(g))

@@ -38,7 +38,8 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
                                        const T* __restrict__ kv_pages, const int* __restrict__ block_table,
                                        int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                        int n_seqs, int nq, int nkv, int d, int page_size, int n_pages, int window,
-                                       float scale, int TQ, int GS, int dv, int row, const float* __restrict__ sinks) {
+                                       float scale, int TQ, int GS, int dv, int row, const float* __restrict__ sinks,
+                                       int chunk) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int G = nq / nkv;
@@ -94,7 +95,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
   }
 
   int first_key = 0;
-  if (window > 0) first_key = max(0, pos_lo - window + 1);
+  first_key = nhv_first_key(pos_lo, window, chunk);
   const int c_begin = (first_key / AT_CHUNK) * AT_CHUNK;
 
   for (int c0 = c_begin; c0 <= pos_hi; c0 += AT_CHUNK) {
@@ -133,7 +134,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
       if (p >= n_pairs) break;
       const int tq = p / gs;
       const int pos = pos_lo + tq;
-      const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+      const int lo = nhv_first_key(pos, window, chunk);
       if (c0 > pos || c0 + AT_CHUNK <= lo) continue;  // no key of this chunk is visible to this query
       const int j = c0 + lane;
       float s = -INFINITY;
@@ -187,7 +188,7 @@ __global__ void attn_paged_simt_kernel(const T* __restrict__ q, int q_stride, T*
 NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* out, int out_stride,
                                   const void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
                                   const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int dv, int row,
-                                  int page_size, int n_pages, int window, float scale, const float* sinks,
+                                  int page_size, int n_pages, int window, int chunk, float scale, const float* sinks,
                                   cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
@@ -209,7 +210,7 @@ NHV_API int nhv_attention_simt_ex(int dtype, const void* q, int q_stride, void* 
                                     (int)smem), "attention");                                                  \
     nhv_launch(attn_paged_simt_kernel<T>, grid, AT_WARPS * 32, smem, stream,                                   \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv_pages, block_table, bt_stride, cu_q, kv_len,  \
-        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks);                        \
+        n_seqs, nq, nkv, d, page_size, n_pages, window, scale, TQ, GS, dv, row, sinks, chunk);                      \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
@@ -224,5 +225,5 @@ NHV_API int nhv_attention_simt(int dtype, const void* q, int q_stride, void* out
                                const int* kv_len, int n_seqs, int n_tokens, int nq, int nkv, int d, int page_size,
                                int n_pages, int window, float scale, cudaStream_t stream) {
   return nhv_attention_simt_ex(dtype, q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len,
-                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, scale, nullptr, stream);
+                               n_seqs, n_tokens, nq, nkv, d, d, d, page_size, n_pages, window, 0, scale, nullptr, stream);
 }

@@ -125,6 +125,20 @@ __device__ __forceinline__ float f2_sum(f32x2 a, f32x2 b) {     // (a.lo + a.hi)
   return (x + y) + (z + w);
 }
 
+// The first key that a query at position pos may see besides causality: with a sliding window the last `window`
+// keys (window > 0), with chunked attention the keys of its own chunk of `chunk` positions counted from position 0
+// (chunk > 0); both 0: every key.  The result does not fall as pos grows, so the bound of a block's first row
+// holds for the block.
+__host__ __device__ __forceinline__ int nhv_first_key(int pos, int window, int chunk) {
+  if (pos < 0) return 0;
+  int lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+  if (chunk > 0) {
+    const int c = (pos / chunk) * chunk;
+    lo = c > lo ? c : lo;
+  }
+  return lo;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

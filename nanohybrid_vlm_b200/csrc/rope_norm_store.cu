@@ -7,6 +7,9 @@
 //   k heads: the same -> the token's slot of the K pages
 //   v heads: copied -> the token's slot of the V pages
 // eps < 0 leaves the norm out.  Rotation and norm are computed in fp32 and rounded once.
+// bias (optional, [nq*dk + nkv*dk], the query and key columns of qkv): added in fp32 to what the projection gave,
+// before anything else (projected values have none).  v_from_k: the values are the key heads as projected (with their bias, before the rotation); qkv
+// then has no value columns and dv == dk.
 // Cache pages of one layer: [page][K|V][kv_head][slot_in_page][row], row >= max(dk, dv); the elements of a row
 // beyond the head's size are cleared.  slot_mapping[t] = page * page_size + slot_in_page, or -1 for "do not store".
 #include "nhv_common.cuh"
@@ -20,7 +23,8 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
                                        const int* __restrict__ slot_mapping, const int* __restrict__ positions,
                                        const float* __restrict__ cos_sin, int rotary_dim, int max_position,
                                        int n_tokens, int nq, int nkv, int dk, int dv, int row, int page_size,
-                                       int n_pages, float eps, int heads_per_token) {
+                                       int n_pages, float eps, int heads_per_token, const T* __restrict__ bias,
+                                       int v_from_k) {
   extern __shared__ float smem[];
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -31,8 +35,9 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
   float* v = smem + warp * RN_MAX_D;
   const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);  // q, k, v
   const int d = kind == 2 ? dv : dk;
-  const T* src = qkv + (size_t)t * qkv_stride + (kind == 2 ? (size_t)(nq + nkv) * dk + (size_t)(head - nq - nkv) * dv
-                                                           : (size_t)head * dk);
+  const size_t col0 = kind == 2 ? (v_from_k ? (size_t)(head - nkv) * dk : (size_t)(nq + nkv) * dk + (size_t)(head - nq - nkv) * dv)
+                                : (size_t)head * dk;
+  const T* src = qkv + (size_t)t * qkv_stride + col0;
   T* dst;
   int width = d;
   if (kind == 0) {
@@ -45,7 +50,11 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
     dst = kv_pages + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + off) * row;
     width = row;
   }
-  for (int c = lane; c < d; c += 32) v[c] = to_f32<T>(src[c]);
+  if (bias && (kind != 2 || v_from_k)) {
+    for (int c = lane; c < d; c += 32) v[c] = to_f32<T>(src[c]) + to_f32<T>(bias[col0 + c]);
+  } else {
+    for (int c = lane; c < d; c += 32) v[c] = to_f32<T>(src[c]);
+  }
   __syncwarp();
   float ss = 0.f;
   float mine[RN_MAX_D / 32];
@@ -85,7 +94,8 @@ __global__ void rope_norm_store_kernel(const T* __restrict__ qkv, int qkv_stride
 NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void* q_out, int q_out_stride,
                                 void* kv_pages, const int* slot_mapping, const int* positions, const float* cos_sin,
                                 int rotary_dim, int max_position, int n_tokens, int nq, int nkv, int dk, int dv, int row,
-                                int page_size, int n_pages, float eps, cudaStream_t stream) {
+                                int page_size, int n_pages, float eps, const void* bias, int v_from_k,
+                                cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(n_tokens > 0 && nq > 0 && nkv >= 0 && dk > 0 && dv > 0, "rope_norm_store: bad sizes");
   NHV_REQUIRE(dk <= RN_MAX_D && dv <= RN_MAX_D, "rope_norm_store: head sizes %d / %d are beyond the supported %d", dk, dv, RN_MAX_D);
@@ -94,6 +104,7 @@ NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void
   NHV_REQUIRE(kv_pages == nullptr || (page_size > 0 && n_pages > 0 && slot_mapping && row >= dk && row >= dv),
               "rope_norm_store: a key/value store needs pages whose rows hold a head, and a slot mapping");
   NHV_REQUIRE(!cos_sin || positions, "rope_norm_store: rotation needs positions");
+  NHV_REQUIRE(!v_from_k || dv == dk, "rope_norm_store: values taken from the keys have the keys' size, not %d", dv);
   const int heads_per_token = kv_pages ? nq + 2 * nkv : nq;
   const long items = (long)n_tokens * heads_per_token;
   const int blocks = (int)((items + RN_WARPS - 1) / RN_WARPS);
@@ -101,7 +112,7 @@ NHV_API int nhv_rope_norm_store(int dtype, const void* qkv, int qkv_stride, void
 #define LAUNCH(T)                                                                                                  \
   nhv_launch(rope_norm_store_kernel<T>, blocks, RN_WARPS * 32, smem, stream, (const T*)qkv, qkv_stride, (T*)q_out, \
              q_out_stride, (T*)kv_pages, slot_mapping, positions, cos_sin, rotary_dim, max_position, n_tokens, nq, \
-             nkv, dk, dv, row, page_size, n_pages, eps, heads_per_token)
+             nkv, dk, dv, row, page_size, n_pages, eps, heads_per_token, (const T*)bias, v_from_k)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
   else NHV_REQUIRE(false, "rope_norm_store: unknown dtype %d", dtype);

@@ -16,7 +16,7 @@
 // gated_rmsnorm: rows of fp32 values y [T, n_groups * size], a gate z in the storage type, a weight w:
 //   gate_first:  out = unit_rms(y * silu(z)) * w          (each group of `size` by its own root mean square)
 //   else:        out = unit_rms(y) * w * silu(z)
-// with w indexed by (column mod w_period).
+// with w indexed by (column mod w_period).  gate_kind 1 puts sigmoid(z) in the place of silu(z).
 #include <math.h>
 
 #include "nhv_common.cuh"
@@ -511,11 +511,16 @@ NHV_API int nhv_ssd_scan(int dtype, float* y, const void* xbc, int xbc_stride, c
   return 0;
 }
 
+__device__ __forceinline__ float gn_gate(float g, int kind) {
+  const float sg = 1.0f / (1.0f + expf(-g));
+  return kind == 1 ? sg : g * sg;
+}
+
 // One block per (token, group).
 template <typename T>
 __global__ void gated_rmsnorm_kernel(T* __restrict__ out, int out_stride, const float* __restrict__ y,
                                      const T* __restrict__ z, int z_stride, const T* __restrict__ w, int w_period,
-                                     int n_groups, int size, float eps, int gate_first) {
+                                     int n_groups, int size, float eps, int gate_first, int gate_kind) {
   __shared__ float red[33];
   pdl_prologue();
   const int t = blockIdx.x / n_groups, gidx = blockIdx.x % n_groups;
@@ -526,16 +531,14 @@ __global__ void gated_rmsnorm_kernel(T* __restrict__ out, int out_stride, const 
   for (int c = threadIdx.x; c < size; c += blockDim.x) {
     float v = yr[c];
     if (gate_first) {
-      const float g = to_f32<T>(zr[c]);
-      v *= g / (1.0f + expf(-g));
+      v *= gn_gate(to_f32<T>(zr[c]), gate_kind);
     }
     ss = fmaf(v, v, ss);
   }
   const float total = block_sum(ss, red);
   const float rstd = 1.0f / sqrtf(total / (float)size + eps);
   for (int c = threadIdx.x; c < size; c += blockDim.x) {
-    const float g = to_f32<T>(zr[c]);
-    const float sg = g / (1.0f + expf(-g));
+    const float sg = gn_gate(to_f32<T>(zr[c]), gate_kind);
     const float wv = to_f32<T>(w[(gidx * size + c) % w_period]);
     dst[c] = from_f32<T>(yr[c] * sg * rstd * wv);
   }
@@ -549,7 +552,8 @@ constexpr int GN_MAX = 256;
 template <typename T>
 __global__ void __launch_bounds__(GN_WARPS * 32) gated_rmsnorm_warp_kernel(
     T* __restrict__ out, int out_stride, const float* __restrict__ y, const T* __restrict__ z, int z_stride,
-    const T* __restrict__ w, int w_period, long n_items, int n_groups, int size, float eps, int gate_first) {
+    const T* __restrict__ w, int w_period, long n_items, int n_groups, int size, float eps, int gate_first,
+    int gate_kind) {
   pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long item = (long)blockIdx.x * GN_WARPS + warp;
@@ -565,8 +569,7 @@ __global__ void __launch_bounds__(GN_WARPS * 32) gated_rmsnorm_warp_kernel(
   for (int k = 0; k < GN_MAX / 32; ++k) {
     const int c = lane + k * 32;
     if (c < size) {
-      const float g = to_f32<T>(zr[c]);
-      const float sg = g / (1.0f + expf(-g));
+      const float sg = gn_gate(to_f32<T>(zr[c]), gate_kind);
       const float v = gate_first ? yr[c] * sg : yr[c];
       vals[k] = v;
       gates[k] = gate_first ? 1.0f : sg;
@@ -583,7 +586,7 @@ __global__ void __launch_bounds__(GN_WARPS * 32) gated_rmsnorm_warp_kernel(
 
 NHV_API int nhv_gated_rmsnorm(int dtype, void* out, int out_stride, const float* y, const void* z, int z_stride,
                               const void* w, int w_period, int n_tokens, int n_groups, int size, float eps,
-                              int gate_first, cudaStream_t stream) {
+                              int gate_first, int gate_kind, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(n_groups > 0 && size > 0 && w_period > 0, "gated_rmsnorm: bad sizes");
   if (size <= GN_MAX) {           // larger groups: a block per (token, group) below
@@ -592,11 +595,11 @@ NHV_API int nhv_gated_rmsnorm(int dtype, void* out, int out_stride, const float*
     NHV_REQUIRE(wblocks < (1L << 31), "gated_rmsnorm: too many rows");
     if (dtype == NHV_F32)
       nhv_launch(gated_rmsnorm_warp_kernel<float>, (int)wblocks, GN_WARPS * 32, 0, stream, (float*)out, out_stride, y,
-                 (const float*)z, z_stride, (const float*)w, w_period, items, n_groups, size, eps, gate_first);
+                 (const float*)z, z_stride, (const float*)w, w_period, items, n_groups, size, eps, gate_first, gate_kind);
     else if (dtype == NHV_BF16)
       nhv_launch(gated_rmsnorm_warp_kernel<__nv_bfloat16>, (int)wblocks, GN_WARPS * 32, 0, stream, (__nv_bfloat16*)out,
                  out_stride, y, (const __nv_bfloat16*)z, z_stride, (const __nv_bfloat16*)w, w_period, items, n_groups, size,
-                 eps, gate_first);
+                 eps, gate_first, gate_kind);
     else
       NHV_REQUIRE(false, "gated_rmsnorm: unknown dtype %d", dtype);
     NHV_CHECK_LAUNCH("gated_rmsnorm");
@@ -608,10 +611,10 @@ NHV_API int nhv_gated_rmsnorm(int dtype, void* out, int out_stride, const float*
   NHV_REQUIRE(blocks < (1L << 31), "gated_rmsnorm: too many rows");
   if (dtype == NHV_F32)
     nhv_launch(gated_rmsnorm_kernel<float>, (int)blocks, threads, 0, stream, (float*)out, out_stride, y, (const float*)z,
-               z_stride, (const float*)w, w_period, n_groups, size, eps, gate_first);
+               z_stride, (const float*)w, w_period, n_groups, size, eps, gate_first, gate_kind);
   else if (dtype == NHV_BF16)
     nhv_launch(gated_rmsnorm_kernel<__nv_bfloat16>, (int)blocks, threads, 0, stream, (__nv_bfloat16*)out, out_stride, y,
-               (const __nv_bfloat16*)z, z_stride, (const __nv_bfloat16*)w, w_period, n_groups, size, eps, gate_first);
+               (const __nv_bfloat16*)z, z_stride, (const __nv_bfloat16*)w, w_period, n_groups, size, eps, gate_first, gate_kind);
   else
     NHV_REQUIRE(false, "gated_rmsnorm: unknown dtype %d", dtype);
   NHV_CHECK_LAUNCH("gated_rmsnorm");

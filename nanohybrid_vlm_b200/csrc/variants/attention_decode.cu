@@ -287,7 +287,7 @@ struct alignas(64) Params {
   float* part_ml;           // [grid][2][16][2]
   int* counters;            // [n_seqs * head_blocks], zero; left zero
   const float* sinks;       // per query head, or null: exp(sink) joins the softmax denominator once, where a head's sum is final
-  int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window;
+  int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, chunk;
   float scale_log2;
   FusedQK fq;
 };
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  const int n_seqs = p.n_seqs, nkv = p.nkv, page_size = p.page_size, window = p.window;
+  const int n_seqs = p.n_seqs, nkv = p.nkv, page_size = p.page_size, window = p.window, chunk = p.chunk;
   const int G = p.nq / nkv;
   const int rows_per = min(G, 16);
   const int chunks = (G + 15) / 16;                          // groups of more than 16 heads: several head blocks
@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     }
     int nt = 0, idle = 0;
     if (single) {
-      const int lo = window > 0 ? max(0, total - window) : 0;
+      const int lo = nhv_first_key(total - 1, window, chunk);
       nt = total > 0 ? (total - 1) / BN - lo / BN + 1 : 0;
       // An entry that only fills the batch up to a fixed shape has no page for its token: it costs nothing here
       // (no tiles, no piece) and its output rows are cleared.
@@ -465,7 +465,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
       if (pc.n_tiles == 0) continue;
       const int kvh = pc.hb / chunks;
       const int total = s_total[pc.seq];
-      const int lo = window > 0 ? max(0, total - window) : 0;
+      const int lo = nhv_first_key(total - 1, window, chunk);
       const int key_begin = (lo / BN + pc.t_begin) * BN;
       const int* table = p.block_table + (size_t)pc.seq * p.bt_stride;
       for (int it0 = 0; it0 < pc.n_tiles && ok; it0 += 32) {
@@ -531,7 +531,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const __grid_co
     const int kvh = hb / chunks, g0 = (hb - kvh * chunks) * 16;
     const int gn = min(rows_per, G - g0);
     const int total = s_total[seq];
-    const int lo = window > 0 ? max(0, total - window) : 0;
+    const int lo = nhv_first_key(total - 1, window, chunk);
     const int key_begin = (lo / BN + pc.t_begin) * BN;
     const size_t tok = s_tok[seq];
     const bool has_last = pc.t_begin + n_tiles == nt;         // this piece ends with the request's newest key
@@ -811,7 +811,7 @@ NHV_API int NHV_FN(nhv_attn_decode_blocks_d)() {
 NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* qkv, int qkv_stride, void* out, int out_stride,
                                       void* kv_pages, const int* block_table, int bt_stride, const int* cu_q,
                                       const int* kv_len, int n_seqs, int nq, int nkv, int page_size, int n_pages,
-                                      int window, float scale, float* part_o, float* part_ml, int* counters,
+                                      int window, int chunk, float scale, float* part_o, float* part_ml, int* counters,
                                       const void* q_w, const void* k_w, const float* cos_sin, const int* positions,
                                       const int* slot_mapping, int rotary_dim, int max_position, int store, float eps,
                                       float weight_offset, const float* sinks, cudaStream_t stream) {
@@ -893,7 +893,7 @@ NHV_API int NHV_FN(nhv_attn_decode_d)(const void* q, int q_stride, const void* q
   p.counters = counters;
   p.sinks = sinks;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv;
-  p.page_size = page_size; p.n_pages = n_pages; p.window = window;
+  p.page_size = page_size; p.n_pages = n_pages; p.window = window; p.chunk = chunk;
   p.scale_log2 = scale * LOG2E;
   const cudaError_t launched = deep ? nhv_launch(attn_decode_kernel<STAGES_DEEP, 8>, dim3(blocks), dim3(THREADS), smem, stream, p)
                                     : nhv_launch(attn_decode_kernel<STAGES_MIN, 16>, dim3(blocks), dim3(THREADS), smem, stream, p);

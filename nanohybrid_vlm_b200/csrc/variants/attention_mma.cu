@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
     const bf16* __restrict__ kv_pages, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int nq, int nkv, int page_size,
-    int n_pages, int window, float scale_log2, int tokens_per_block, const float* __restrict__ sinks) {
+    int n_pages, int window, int chunk, float scale_log2, int tokens_per_block, const float* __restrict__ sinks) {
   constexpr int PF_ROWS = 64 * MTW;                          // rows (token x head of the group) per block
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qbuf = reinterpret_cast<bf16*>(smem_raw);            // [PF_ROWS rows]
@@ -377,20 +377,20 @@ __global__ void __launch_bounds__(THREADS, MTW == 2 ? 2 : (D <= 128 ? 3 : 1)) at
       const int tq = R / G;
       if (tq < tq_n) {
         row_hi[mt][i] = pos0 + tq;
-        row_lo[mt][i] = window > 0 ? max(0, row_hi[mt][i] - window + 1) : 0;
+        row_lo[mt][i] = nhv_first_key(row_hi[mt][i], window, chunk);
       } else {
         row_hi[mt][i] = -1;
         row_lo[mt][i] = 0;
       }
     }
   const int pos_hi = pos0 + tq_n - 1;
-  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int first_key = nhv_first_key(pos0, window, chunk);
   const int key_begin = (first_key / BN) * BN;
   const int n_tiles = (pos_hi - key_begin) / BN + 1;
   // this warp's rows: the span of keys any of them sees (warp-uniform, so whole tiles can be skipped)
   const int w_tq_lo = (warp * WROWS) / G, w_tq_hi = min((warp * WROWS + WROWS - 1) / G, tq_n - 1);
   const int w_hi = w_tq_lo < tq_n ? pos0 + w_tq_hi : -1;
-  const int w_lo = window > 0 ? max(0, pos0 + w_tq_lo - window + 1) : 0;
+  const int w_lo = nhv_first_key(pos0 + w_tq_lo, window, chunk);
 
   PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
   PrefillState<MTW> st;
@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride, const bf16* __restrict__ kv_pages,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int n_seqs, int nq, int nkv,
-    int page_size, int n_pages, int window, float scale_log2, int max_pieces, const FusedQK fq,
+    int page_size, int n_pages, int window, int chunk, float scale_log2, int max_pieces, const FusedQK fq,
     const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);
@@ -545,7 +545,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     int nt = 0;
     if (cu_q[sq + 1] - cu_q[sq] == 1) {
       const int total = kv_len[sq];
-      const int lo = window > 0 ? max(0, total - window) : 0;
+      const int lo = nhv_first_key(total - 1, window, chunk);
       nt = (total - 1) / BN - lo / BN + 1;
     }
     s_cnt[sq] = (unsigned short)min(nt, 65535);
@@ -595,7 +595,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? (DSTAGES == 2 ? 3 : 2) : 1
     const int kvh = hb / chunks, g0 = (hb - kvh * chunks) * 16;
     const int gn = min(rows_per, G - g0);
     const int total = kv_len[seq];
-    const int lo = window > 0 ? max(0, total - window) : 0;
+    const int lo = nhv_first_key(total - 1, window, chunk);
     const int key_begin = (lo / BN + t_begin) * BN;
     const size_t tok = cu_q[seq];
     PageGeom geom{kv_pages, block_table + (size_t)seq * bt_stride, nkv, kvh, page_size, n_pages};
@@ -839,7 +839,7 @@ NHV_API int NHV_FN(nhv_attn_mma_tile_d)() { return BN; }
 static int attention_launch(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
                             const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                             int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
-                            int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
+                            int nkv, int page_size, int n_pages, int window, int chunk, float scale, float* scratch_o,
                             float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
                             const FusedQK& fq, const float* sinks, cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
@@ -881,12 +881,12 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
       if (wide)
         nhv_launch(attn_prefill_kernel<2>, grid, THREADS, prefill_smem_bytes<2>(), stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-            n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block, sinks);
+            n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks);
     }
     if (!wide)
       nhv_launch(attn_prefill_kernel<1>, grid, THREADS, prefill_smem_bytes<1>(), stream,
           (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-          n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, tokens_per_block, sinks);
+          n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, tokens_per_block, sinks);
   }
   if (n_decode_seqs > 0) {
     ATT_REQUIRE(scratch_o && scratch_ml && counters && max_pieces > 0 && decode_blocks > 0,
@@ -903,7 +903,7 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
     decode_blocks = resident;
     nhv_launch(attn_decode_kernel, dim3(decode_blocks), THREADS, kDecodeSmemBytes, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv_pages, block_table, bt_stride, cu_q, kv_len,
-        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, scale_log2, max_pieces, fq, sinks);
+        scratch_o, scratch_ml, counters, n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale_log2, max_pieces, fq, sinks);
   }
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
@@ -916,12 +916,12 @@ static int attention_launch(const void* q, int q_stride, void* out, int out_stri
 NHV_API int NHV_FN(nhv_attn_mma_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
                                    const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                                    int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int n_decode_seqs, int nq,
-                                   int nkv, int page_size, int n_pages, int window, float scale, float* scratch_o,
+                                   int nkv, int page_size, int n_pages, int window, int chunk, float scale, float* scratch_o,
                                    float* scratch_ml, int* counters, int max_pieces, int decode_blocks,
                                    const float* sinks, cudaStream_t stream) {
   FusedQK none = {};
   return attention_launch(q, q_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs,
-                          n_prefill_tokens, n_prefill_seqs, n_decode_seqs, nq, nkv, page_size, n_pages, window, scale,
+                          n_prefill_tokens, n_prefill_seqs, n_decode_seqs, nq, nkv, page_size, n_pages, window, chunk, scale,
                           scratch_o, scratch_ml, counters, max_pieces, decode_blocks, none, sinks, stream);
 }
 
@@ -933,7 +933,7 @@ NHV_API int NHV_FN(nhv_attn_mma_can_fuse_d)() { return D % 32 == 0 ? 1 : 0; }
 // what qk_norm_rope_store would have done before it.  q_w / k_w null: no norm; cos_sin null: no rotation.
 NHV_API int NHV_FN(nhv_attn_mma_decode_fused_d)(const void* qkv, int qkv_stride, void* out, int out_stride, void* kv_pages,
                                                 const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
-                                                int n_seqs, int nq, int nkv, int page_size, int n_pages, int window,
+                                                int n_seqs, int nq, int nkv, int page_size, int n_pages, int window, int chunk,
                                                 float scale, float* scratch_o, float* scratch_ml, int* counters,
                                                 int max_pieces, const void* q_w, const void* k_w, const float* cos_sin,
                                                 const int* positions, const int* slot_mapping, int rotary_dim,
@@ -958,6 +958,6 @@ NHV_API int NHV_FN(nhv_attn_mma_decode_fused_d)(const void* qkv, int qkv_stride,
   fq.eps = eps;
   fq.weight_offset = weight_offset;
   return attention_launch(qkv, qkv_stride, out, out_stride, kv_pages, block_table, bt_stride, cu_q, kv_len, n_seqs, 0, 0,
-                          n_seqs, nq, nkv, page_size, n_pages, window, scale, scratch_o, scratch_ml, counters, max_pieces,
+                          n_seqs, nq, nkv, page_size, n_pages, window, chunk, scale, scratch_o, scratch_ml, counters, max_pieces,
                           1, fq, nullptr, stream);
 }

@@ -162,7 +162,7 @@ struct alignas(64) Params {
   const int* cu_q;
   const int* kv_len;
   const float* sinks;     // per query head, or null: exp(sink) joins the softmax denominator (no key, no value, no scale)
-  int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, tokens_per_block;
+  int q_stride, out_stride, bt_stride, n_seqs, nq, nkv, page_size, n_pages, window, chunk, tokens_per_block;
   float scale_log2;
 };
 
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     pos0 = total - n_new + t0;
   }
   const int pos_hi = pos0 + tq_n - 1;
-  const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int first_key = nhv_first_key(pos0, p.window, p.chunk);
   const int key_begin = (first_key / BN) * BN;
   const int n_tiles = active ? (pos_hi - key_begin) / BN + 1 : 0;
 
@@ -334,10 +334,10 @@ __global__ void __launch_bounds__(THREADS, (2 * BN + D) <= 256 ? 2 : 1) attn_tcg
     const int tq = R / G, g = R - tq * G;
     const bool valid = tq < tq_n;
     const int row_hi = valid ? pos0 + tq : -1;
-    const int row_lo = p.window > 0 ? max(0, row_hi - p.window + 1) : 0;
+    const int row_lo = nhv_first_key(row_hi, p.window, p.chunk);
     // the block's rows: keys up to pos0 are in sight of every valid row if they are above the highest lower edge
     const int all_hi = (tq_n * G >= BM) ? pos0 : -1;            // with padding rows every tile is masked
-    const int all_lo = p.window > 0 ? max(0, pos_hi - p.window + 1) : 0;
+    const int all_lo = nhv_first_key(pos_hi, p.window, p.chunk);
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     float m_run = -INFINITY, l = 0.f;
     bool ok = true;
@@ -511,7 +511,7 @@ NHV_API void* NHV_FN(nhv_attn_tcgen05_error_word_d)() { return nhv_wait_error_ad
 NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, int out_stride, const void* kv_pages,
                                        const int* block_table, int bt_stride, const int* cu_q, const int* kv_len,
                                        int n_seqs, int n_prefill_tokens, int n_prefill_seqs, int nq, int nkv,
-                                       int page_size, int n_pages, int window, float scale, const float* sinks,
+                                       int page_size, int n_pages, int window, int chunk, float scale, const float* sinks,
                                        cudaStream_t stream) {
   ATT_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
   const int G = nq / nkv;
@@ -552,6 +552,7 @@ NHV_API int NHV_FN(nhv_attn_tcgen05_d)(const void* q, int q_stride, void* out, i
   p.page_size = page_size;
   p.n_pages = n_pages;
   p.window = window;
+  p.chunk = chunk;
   p.tokens_per_block = BM / G;
   p.scale_log2 = scale * LOG2E;
   const int max_tiles = n_prefill_tokens / p.tokens_per_block + n_prefill_seqs;

@@ -80,7 +80,7 @@ class BatchBuilder:
         self.max_tokens, self.max_seqs, self.max_pages = max_tokens, max_seqs, max_pages_per_seq
         self._layouts: dict = {}
         self._table_rows = None          # (layout, per row (request, table length)) of the last all-decode step
-        self._windows = any(g.window is not None for g in cache_manager.groups)
+        self._windows = any(g.gives_back for g in cache_manager.groups)
         cap = self._layout(max_tokens, max_seqs, max_tokens, max_pages_per_seq)[1]
         self._host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self._np = self._host.numpy()

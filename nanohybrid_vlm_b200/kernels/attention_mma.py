@@ -31,7 +31,7 @@ def get(head_dim: int):
         from ..csrc.build import ensure_variant
         lib = ctypes.CDLL(ensure_variant("attention_mma.cu", {"NHV_ATTN_D": head_dim}))
         fn = getattr(lib, f"nhv_attn_mma_d{head_dim}")
-        fn.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, P, P, P, I, I, P, P]
+        fn.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, P, I, I, P, P]
         fn.restype = c_int
         err = getattr(lib, f"nhv_attn_mma_last_error_d{head_dim}")
         err.restype = ctypes.c_char_p
@@ -39,7 +39,7 @@ def get(head_dim: int):
         split.restype = c_int
 
         fused = getattr(lib, f"nhv_attn_mma_decode_fused_d{head_dim}")
-        fused.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, P, P, P, P, I, I, I, F, F, P]
+        fused.argtypes = [P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, F, P, P, P, I, P, P, P, P, P, I, I, I, F, F, P]
         fused.restype = c_int
         can_fuse = getattr(lib, f"nhv_attn_mma_can_fuse_d{head_dim}")
         can_fuse.restype = c_int

@@ -41,9 +41,20 @@ _SIGNATURES = {
     "nhv_short_conv_silu": [I, I, P, I, P, I, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, P],
     "nhv_delta_rule": [I, P, P, I, P, P, P, P, ctypes.c_long, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P],
     "nhv_ssd_scan": [I, P, P, I, P, I, P, P, P, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, I, I, P],
-    "nhv_gated_rmsnorm": [I, P, I, P, P, I, P, I, I, I, I, F, I, P],
-    "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
-    "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "nhv_gated_rmsnorm": [I, P, I, P, P, I, P, I, I, I, I, F, I, I, P],
+    "nhv_rope_norm_store": [I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, I, P],
+    "nhv_dyntanh": [I, I, I, P, P, P, P, P, I, I, P],
+    "nhv_embed_dyntanh": [I, P, P, P, P, P, P, I, I, I, P],
+    "nhv_dyntanh_stream": [I, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
+    "nhv_sigmoid_mul": [I, P, I, P, I, P, I, I, I, P],
+    "nhv_add_row_bias": [I, P, P, I, I, P],
+    "nhv_clamped_glu": [I, P, P, I, I, F, F, P],
+    "nhv_mlstm_scan": [I, P, P, I, P, I, P, F, P, ctypes.c_long, P, P, P, I, I, I, I, I, P],
+    "nhv_moe_route": [P, P, P, I, P, I, I, I, I, I, P],
+    "nhv_moe_align": [P, I, I, I, P, P, P, P],
+    "nhv_moe_gemm_simt": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
+    "nhv_moe_combine": [I, P, P, P, P, P, I, P, P, P, I, I, I, I, P],
+    "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
 }
 
 

@@ -199,24 +199,216 @@ def ssd_scan(y, xbc, dt_raw, dt_bias, a_log, d_skip, state, batch, H: int, P: in
          SCAN_COLUMNS, stream_ptr())
 
 
-def gated_rmsnorm(out, y, z, weight, n_groups: int, eps: float, gate_first: bool) -> None:
+def gated_rmsnorm(out, y, z, weight, n_groups: int, eps: float, gate_first: bool, gate: str = "silu") -> None:
     """y [T, n_groups * size] float32, gate z [T, same] (a view with unit column stride), weight of any length that
     divides the row (indexed by column mod its length).  gate_first: out = unit_rms(y * silu(z)) * weight per group;
-    else out = unit_rms(y) * weight * silu(z)."""
+    else out = unit_rms(y) * weight * silu(z).  ``gate`` "sigmoid" puts sigmoid(z) in the place of silu(z)."""
+    assert gate in ("silu", "sigmoid")
     _need_cuda(out, y, z, weight)
     T, width = y.shape
     assert y.dtype == torch.float32 and y.is_contiguous() and width % n_groups == 0
     assert z.shape == y.shape and z.stride(1) == 1 and out.shape == y.shape and out.stride(1) == 1
     assert out.dtype == z.dtype == weight.dtype and width % weight.numel() == 0
     call("nhv_gated_rmsnorm", dtype_code(out), out.data_ptr(), out.stride(0), y.data_ptr(), z.data_ptr(), z.stride(0),
-         weight.data_ptr(), weight.numel(), T, n_groups, width // n_groups, float(eps), int(bool(gate_first)), stream_ptr())
+         weight.data_ptr(), weight.numel(), T, n_groups, width // n_groups, float(eps), int(bool(gate_first)),
+         1 if gate == "sigmoid" else 0, stream_ptr())
+
+
+def dyntanh(out, x, alpha, weight, bias) -> None:
+    """out = tanh(alpha * x) * weight + bias (Dynamic Tanh), elementwise over rows of ``weight.numel()`` elements, computed
+    in 32-bit.  ``x`` and ``out`` are each float32 or of the parameters' type; ``alpha`` has one element."""
+    _need_cuda(out, x, alpha, weight, bias)
+    _contig("out", out); _contig("x", x)
+    width = weight.numel()
+    assert alpha.numel() == 1 and bias.numel() == width and alpha.dtype == weight.dtype == bias.dtype
+    assert x.dtype in (torch.float32, weight.dtype) and out.dtype in (torch.float32, weight.dtype) and out.numel() == x.numel()
+    call("nhv_dyntanh", dtype_code(weight), int(x.dtype == torch.float32), int(out.dtype == torch.float32), out.data_ptr(),
+         x.data_ptr(), alpha.data_ptr(), weight.data_ptr(), bias.data_ptr(), x.numel() // width, width, stream_ptr())
+
+
+def embed_dyntanh(out, table, ids, alpha, weight, bias) -> None:
+    """out [T, width] float32 = tanh(alpha * table[ids]) * weight + bias: the looked-up rows through a Dynamic Tanh norm,
+    as the start of a residual stream kept in 32-bit."""
+    _need_cuda(out, table, ids, alpha, weight, bias)
+    _contig("out", out); _contig("table", table)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and out.shape[1] == table.shape[1] == weight.numel()
+    assert alpha.dtype == weight.dtype == bias.dtype == table.dtype
+    call("nhv_embed_dyntanh", dtype_code(table), out.data_ptr(), table.data_ptr(), ids.data_ptr(), alpha.data_ptr(),
+         weight.data_ptr(), bias.data_ptr(), ids.numel(), table.shape[1], table.shape[0], stream_ptr())
+
+
+def dyntanh_stream(out, stream, pre, addend=None, post=None, rows=None, write_stream: bool = True) -> None:
+    """The Dynamic Tanh norm over a float32 residual stream [T, width], with the add of the sub-block before it:
+    s = stream[src] + (tanh(post.alpha * addend[src]) * post.w + post.b, if there is an addend), written back to the
+    stream unless ``rows`` gathers; out[r] = tanh(pre.alpha * s) * pre.w + pre.b rounded once; src = rows[r] or r.
+    ``pre`` / ``post``: (alpha, weight, bias) tensors in the storage type."""
+    tensors = [*pre, *(post or ())]       # post None: the addend is added as it is
+    _need_cuda(out, stream, addend, rows, *tensors)
+    _contig("out", out); _contig("stream", stream)
+    width = stream.shape[-1]
+    assert stream.dtype == torch.float32 and all(t.dtype == out.dtype for t in tensors)
+    assert pre[0].numel() == 1 and pre[1].numel() == pre[2].numel() == width
+    if addend is not None:
+        _contig("addend", addend)
+        assert addend.shape == stream.shape and addend.dtype == out.dtype
+        assert post is None or (post[0].numel() == 1 and post[1].numel() == post[2].numel() == width)
+    n_rows = rows.numel() if rows is not None else stream.numel() // width
+    assert out.numel() == n_rows * width and (rows is None or rows.dtype == torch.int32)
+    pp = post if addend is not None and post is not None else (None, None, None)
+    call("nhv_dyntanh_stream", dtype_code(out), out.data_ptr(), stream.data_ptr(), _ptr(addend), _ptr(pp[0]), _ptr(pp[1]),
+         _ptr(pp[2]), pre[0].data_ptr(), pre[1].data_ptr(), pre[2].data_ptr(), _ptr(rows), n_rows, width,
+         int(bool(write_stream and addend is not None and rows is None)), stream_ptr())
+
+
+def sigmoid_mul(out, x, gate) -> None:
+    """out = x * sigmoid(gate), elementwise in 32-bit; each a [T, width] view with unit column stride."""
+    _need_cuda(out, x, gate)
+    assert out.shape == x.shape == gate.shape and out.dim() == 2 and out.dtype == x.dtype == gate.dtype
+    assert out.stride(1) == x.stride(1) == gate.stride(1) == 1
+    call("nhv_sigmoid_mul", dtype_code(out), out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), gate.data_ptr(),
+         gate.stride(0), x.shape[0], x.shape[1], stream_ptr())
+
+
+def add_row_bias(x, bias) -> None:
+    """x [T, width] += bias [width], in place (the sum in 32-bit)."""
+    _need_cuda(x, bias)
+    _contig("x", x)
+    assert bias.dtype == x.dtype and bias.is_contiguous() and x.shape[-1] == bias.numel()
+    call("nhv_add_row_bias", dtype_code(x), x.data_ptr(), bias.data_ptr(), x.numel() // bias.numel(), bias.numel(), stream_ptr())
+
+
+def clamped_glu(out, gate_up, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit) and u = clamp(up, -limit, limit), for gate_up
+    [n, 2 * inter] with the gate in the first half of each row."""
+    _need_cuda(out, gate_up)
+    _contig("out", out); _contig("gate_up", gate_up)
+    inter = gate_up.shape[-1] // 2
+    assert gate_up.shape[-1] == 2 * inter and out.shape[-1] == inter and out.dtype == gate_up.dtype
+    call("nhv_clamped_glu", dtype_code(out), out.data_ptr(), gate_up.data_ptr(), out.numel() // inter, inter, float(limit),
+         float(alpha), stream_ptr())
+
+
+MLSTM_COLUMN_BLOCK = 16     # columns of the memory that one block of the scan carries (ML_COLS of csrc/mlstm.cu)
+
+
+def mlstm_state_floats(H: int, d: int, dv: int) -> int:
+    """Floats that one request's mLSTM state takes: S [H, dv, d], then per (head, block of columns) the normaliser's d
+    rows and the running maximum (every column block of the scan carries its own copy of them)."""
+    return H * dv * d + H * -(-dv // MLSTM_COLUMN_BLOCK) * (d + 1)
+
+
+def mlstm_scan(y, proj, gates, gate_bias, cap: float, state, batch, H: int, d: int, dv: int) -> None:
+    """The mLSTM recurrence over the step's tokens.  proj [T, >= 2*H*d + H*dv] (q, k, v per head; a view with unit
+    column stride), gates [T, 2*H] float32 (input then forget gates, before bias and cap), gate_bias [2*H] float32,
+    state [slots, mlstm_state_floats] float32 -> y [T, H*dv] float32 (before its norm and gate)."""
+    _need_cuda(y, proj, gates, gate_bias, state)
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and proj.shape[1] >= 2 * H * d + H * dv
+    assert y.dtype == gates.dtype == gate_bias.dtype == state.dtype == torch.float32
+    assert y.is_contiguous() and y.shape == (T, H * dv) and gates.stride(1) == 1 and gates.shape == (T, 2 * H)
+    assert gate_bias.numel() == 2 * H and state.dim() == 2 and state.stride(1) == 1
+    assert state.shape[1] >= mlstm_state_floats(H, d, dv)
+    call("nhv_mlstm_scan", dtype_code(proj), y.data_ptr(), proj.data_ptr(), proj.stride(0), gates.data_ptr(), gates.stride(0),
+         gate_bias.data_ptr(), float(cap), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+         batch.state_slots.data_ptr(), batch.n_seqs, T, H, d, dv, stream_ptr())
+
+
+def moe_route(ids, weights, logits, correction, n_outputs: int, n_groups: int, keep: int) -> None:
+    """The router's choice per token.  logits [T, >= n_outputs] float32 (a view with unit column stride; further columns
+    are not read), correction [n_outputs] float32 or None -> ids [T, top] int32 and weights [T, top] float32.
+    Scores are the softmax over all outputs; the choice is by score + correction among the outputs of the ``keep`` best
+    of ``n_groups`` groups of neighbours (a group's score: its largest choice score); the weights are the chosen scores
+    divided by their sum (+ 1e-20)."""
+    _need_cuda(ids, weights, logits, correction)
+    T, top = ids.shape
+    assert ids.dtype == torch.int32 and weights.dtype == logits.dtype == torch.float32 and weights.shape == ids.shape
+    assert ids.is_contiguous() and weights.is_contiguous() and logits.stride(1) == 1 and logits.shape[0] == T
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == n_outputs)
+    call("nhv_moe_route", ids.data_ptr(), weights.data_ptr(), logits.data_ptr(), logits.stride(0), _ptr(correction), T,
+         n_outputs, n_groups, keep, top, stream_ptr())
+
+
+MOE_TILE_SIMT = 16      # rows of one expert that a block of the CUDA-core products takes (MG_BM of csrc/moe.cu)
+
+
+def moe_sorted_rows(n_slots: int, n_experts: int, tile: int) -> int:
+    """Rows of the by-expert ordering of ``n_slots`` (token, choice) slots: each expert's run is padded to whole tiles."""
+    rows = n_slots + min(n_slots, n_experts) * (tile - 1)
+    return -(-rows // tile) * tile
+
+
+def moe_align(ids, n_experts: int, tile: int):
+    """Order the slots of ids [T, top] by expert (choices >= n_experts, identity experts, take no row).  Returns
+    (sorted_slots [rows] int32: slot of each row or -1, slot_pos [T * top] int32: row of each slot or -1,
+    tile_expert [rows / tile] int32: expert of each tile or -1)."""
+    _need_cuda(ids)
+    n_slots = ids.numel()
+    rows = moe_sorted_rows(n_slots, n_experts, tile)
+    buf = torch.empty(rows + n_slots + rows // tile, dtype=torch.int32, device=ids.device)
+    sorted_slots, slot_pos, tile_expert = buf[:rows], buf[rows:rows + n_slots], buf[rows + n_slots:]
+    call("nhv_moe_align", ids.data_ptr(), n_slots, n_experts, tile, sorted_slots.data_ptr(), slot_pos.data_ptr(),
+         tile_expert.data_ptr(), stream_ptr())
+    return sorted_slots, slot_pos, tile_expert
+
+
+def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: int, limit: float, alpha: float) -> None:
+    """The experts' two products over the ordered rows on the CUDA cores, for any storage type and size, in a fixed order
+    of summation: act [rows, ff] = glu(x[token] gate[e]^T, x[token] up[e]^T), y [rows, width] = act down[e]^T, with
+    gate / up [E, ff, width] and down [E, width, ff]."""
+    _need_cuda(act, y, x, gate, up, down, sorted_slots, tile_expert)
+    for name, t in (("act", act), ("y", y), ("x", x), ("gate", gate), ("up", up), ("down", down)):
+        _contig(name, t)
+    E, ff, width = gate.shape
+    assert up.shape == gate.shape and down.shape == (E, width, ff) and x.shape[1] == width
+    assert act.shape == (sorted_slots.numel(), ff) and y.shape == (sorted_slots.numel(), width)
+    assert act.dtype == y.dtype == x.dtype == gate.dtype == up.dtype == down.dtype
+    tiles = tile_expert.numel()
+    assert tiles * MOE_TILE_SIMT == sorted_slots.numel()
+    call("nhv_moe_gemm_simt", dtype_code(x), 1, act.data_ptr(), x.data_ptr(), width, gate.data_ptr(), up.data_ptr(),
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), stream_ptr())
+    call("nhv_moe_gemm_simt", dtype_code(x), 0, y.data_ptr(), act.data_ptr(), ff, down.data_ptr(), None,
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, stream_ptr())
+
+
+def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
+    """Every chosen expert's output for every token: orders the slots of ids [T, top] by expert and runs the experts' two
+    products over that order.  Returns (y [rows, width], one row per slot that chose a real expert, and slot_pos
+    [T * top] int32, the row of each slot or -1)."""
+    E, ff, width = gate.shape
+    top = ids.shape[1]
+    sorted_slots, slot_pos, tile_expert = moe_align(ids, E, MOE_TILE_SIMT)
+    rows = sorted_slots.numel()
+    act = torch.empty(rows, ff, dtype=x.dtype, device=x.device)
+    y = torch.empty(rows, width, dtype=x.dtype, device=x.device)
+    moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top, limit, alpha)
+    return y, slot_pos
+
+
+def moe_combine(out, y, x, ids, weights, slot_pos, n_experts: int, shared=None, shared_gate=None) -> None:
+    """out[t] = sum over the token's choices of weight * (the expert's row of y, or x[t] itself for an identity expert)
+    (+ sigmoid(shared_gate[t]) * shared[t]; a shared term without a gate counts fully).  ``shared_gate``: a float32
+    column view (one number per token)."""
+    _need_cuda(out, y, x, ids, weights, slot_pos, shared, shared_gate)
+    _contig("out", out); _contig("y", y); _contig("x", x)
+    T, width = x.shape
+    top = ids.shape[1]
+    assert out.shape == x.shape and y.shape[1] == width and out.dtype == y.dtype == x.dtype
+    assert shared is None or (shared.shape == x.shape and shared.dtype == x.dtype and shared.is_contiguous())
+    assert shared_gate is None or (shared is not None and shared_gate.dtype == torch.float32 and shared_gate.shape[0] == T)
+    call("nhv_moe_combine", dtype_code(out), out.data_ptr(), y.data_ptr(), x.data_ptr(), _ptr(shared), _ptr(shared_gate),
+         0 if shared_gate is None else shared_gate.stride(0), ids.data_ptr(), weights.data_ptr(), slot_pos.data_ptr(), T, top,
+         n_experts, width, stream_ptr())
 
 
 def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rotary_dim: int, nq: int, nkv: int, dk: int,
-                    dv: int, eps: float | None) -> None:
+                    dv: int, eps: float | None, bias=None, values_from_keys: bool = False) -> None:
     """qkv [T, nq*dk + nkv*dk + nkv*dv] -> q_out [T, nq*dk] (rotated, then scaled to unit root mean square; eps None:
-    no norm) and K / V rows in kv_pages [pages, 2, nkv, page_size, row] at slot_mapping.  kv_pages None: queries only."""
-    _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin)
+    no norm) and K / V rows in kv_pages [pages, 2, nkv, page_size, row] at slot_mapping.  kv_pages None: queries only.
+    ``bias`` (one element per query and key column of qkv, in its type) is added in 32-bit before the rotation.
+    ``values_from_keys``: the stored values are the key heads as projected (bias added, not rotated); qkv then ends
+    with the keys (it may have further columns that this op does not read) and dv == dk."""
+    _need_cuda(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, bias)
+    assert bias is None or (bias.dtype == qkv.dtype and bias.is_contiguous() and bias.numel() == nq * dk + nkv * dk)
     assert qkv.stride(-1) == 1 and q_out.stride(-1) == 1 and qkv.dim() == 2 and q_out.dim() == 2
     n_tokens = qkv.shape[0]
     if kv_pages is not None:
@@ -232,13 +424,15 @@ def rope_norm_store(qkv, q_out, kv_pages, slot_mapping, positions, cos_sin, rota
     call("nhv_rope_norm_store", dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), q_out.data_ptr(), q_out.stride(0),
          _ptr(kv_pages), _ptr(slot_mapping), _ptr(positions), _ptr(cos_sin), int(rotary_dim),
          0 if cos_sin is None else cos_sin.shape[0], n_tokens, nq, nkv, dk, dv, row, page_size, n_pages,
-         -1.0 if eps is None else float(eps), stream_ptr())
+         -1.0 if eps is None else float(eps), _ptr(bias), int(bool(values_from_keys)), stream_ptr())
 
 
 def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_tokens: int, nq: int, nkv: int,
-                        dk: int, dv: int, scale: float, sinks=None, window: int = 0) -> None:
+                        dk: int, dv: int, scale: float, sinks=None, window: int = 0, chunk: int = 0) -> None:
     """Causal attention of this step's tokens over the pages with key heads of dk and value heads of dv elements:
-    q [T, nq*dk] -> out [T, nq*dv].  ``sinks`` [nq] float32: a term exp(sink) in each head's softmax denominator."""
+    q [T, nq*dk] -> out [T, nq*dv].  ``sinks`` [nq] float32: a term exp(sink) in each head's softmax denominator.
+    ``window`` > 0: the last ``window`` keys only; ``chunk`` > 0: only the keys of the query's own chunk of ``chunk``
+    positions, counted from position 0 of the request."""
     _need_cuda(out, q, kv_pages, block_table, cu_q, kv_len, sinks)
     _contig("kv_pages", kv_pages)
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and out.dtype == q.dtype == kv_pages.dtype
@@ -248,14 +442,15 @@ def attention_sink_simt(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == nq)
     call("nhv_attention_simt_ex", dtype_code(q), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
          kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(),
-         n_seqs, n_tokens, nq, nkv, dk, dv, row, page_size, n_pages, int(window), float(scale), _ptr(sinks), stream_ptr())
+         n_seqs, n_tokens, nq, nkv, dk, dv, row, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks),
+         stream_ptr())
 
 
 SINK_ATTENTION_ON_TENSOR_CORES = True     # tests switch it off to compare with the CUDA-core kernel at the same shapes
 
 
 def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, dv: int, scale: float, sinks=None,
-                   window: int = 0) -> None:
+                   window: int = 0, chunk: int = 0) -> None:
     """Attention of the step's tokens over the cache for layers with a sink and / or value heads of another size
     than their key heads: picks the kernel for the dtype and sizes.  bfloat16 with key and value heads of one size
     (in steps of 16) runs on the tensor cores like ``attention``; float32 and unequal head sizes on the CUDA cores."""
@@ -263,10 +458,10 @@ def attention_sink(out, q, kv_pages, tables, batch, nq: int, nkv: int, dk: int, 
             and attention_mma.supports(dk, nq, nkv, batch.n_seqs)):
         attention_tensor_core(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs,
                               batch.n_prefill_tokens, batch.n_prefill_seqs, batch.n_decode_seqs, batch.max_kv_len,
-                              nq, nkv, dk, scale, window, sinks)
+                              nq, nkv, dk, scale, window, sinks, chunk)
         return
     attention_sink_simt(out, q, kv_pages, tables.block_tables, batch.cu_q, batch.kv_len, batch.n_seqs, batch.n_tokens,
-                        nq, nkv, dk, dv, scale, sinks, window)
+                        nq, nkv, dk, dv, scale, sinks, window, chunk)
 
 
 def linear_f32(out, x, weight) -> None:
@@ -375,7 +570,7 @@ def _tma_decode_scratch(device, head_dim: int, blocks: int):
 def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_kv_len, n_seqs: int, nq: int, nkv: int,
                           head_dim: int, scale: float, window: int, q_weight=None, k_weight=None, cos_sin=None,
                           positions=None, slot_mapping=None, rotary_dim: int = 0, eps: float = 0.0,
-                          weight_offset: float = 0.0, store: bool = False, sinks=None) -> None:
+                          weight_offset: float = 0.0, store: bool = False, sinks=None, chunk: int = 0) -> None:
     launch, blocks = attention_decode.get(head_dim)
     n_pages, two, h, page_size, d = kv_pages.shape
     group = nq // nkv
@@ -385,7 +580,7 @@ def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_
     library.LAUNCHES += 1
     launch(_ptr(q), 0 if q is None else q.stride(0), _ptr(qkv), 0 if qkv is None else qkv.stride(0), out.data_ptr(),
            out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), batch_cu_q.data_ptr(),
-           batch_kv_len.data_ptr(), n_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), part_o.data_ptr(),
+           batch_kv_len.data_ptr(), n_seqs, nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), part_o.data_ptr(),
            part_ml.data_ptr(), counters.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), _ptr(positions),
            _ptr(slot_mapping), int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0], 1 if store else 0, float(eps),
            float(weight_offset), _ptr(sinks), stream_ptr())
@@ -393,7 +588,7 @@ def _attention_decode_tma(out, q, qkv, kv_pages, block_table, batch_cu_q, batch_
 
 def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int, head_dim: int, scale: float,
                            window: int, q_weight, k_weight, cos_sin, rotary_dim: int, eps: float,
-                           weight_offset: float, store: bool) -> bool:
+                           weight_offset: float, store: bool, chunk: int = 0) -> bool:
     """A step of single tokens only, in bfloat16: attention straight from the projection's output.  The decode
     kernel norms and rotates the new query and key heads itself and stores the new keys and values (what
     ``qk_norm_rope_store`` does otherwise, in a launch of its own).  Returns False, having done nothing, when
@@ -416,7 +611,7 @@ def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int,
     if USE_TMA_DECODE and attention_decode.supports(head_dim, nq, nkv, page_size, n_seqs):
         _attention_decode_tma(out, None, qkv, kv_pages, block_table, batch.cu_q, batch.kv_len, n_seqs, nq, nkv, head_dim,
                               scale, window, q_weight, k_weight, cos_sin, batch.positions, tables.slot_mapping, rotary_dim,
-                              eps, weight_offset, store)
+                              eps, weight_offset, store, chunk=chunk)
         return True
     launch_fused = attention_mma.get(head_dim)[2]
     if launch_fused is None:
@@ -431,7 +626,7 @@ def attention_decode_fused(out, qkv, kv_pages, tables, batch, nq: int, nkv: int,
     library.LAUNCHES += 1
     launch_fused(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
                  block_table.stride(0), batch.cu_q.data_ptr(), batch.kv_len.data_ptr(), n_seqs, nq, nkv, page_size,
-                 n_pages, int(window), float(scale), scratch_o.data_ptr(), scratch_ml.data_ptr(), counters.data_ptr(),
+                 n_pages, int(window), int(chunk), float(scale), scratch_o.data_ptr(), scratch_ml.data_ptr(), counters.data_ptr(),
                  max_pieces, _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), batch.positions.data_ptr(),
                  tables.slot_mapping.data_ptr(), int(rotary_dim), 0 if cos_sin is None else cos_sin.shape[0],
                  1 if store else 0, float(eps), float(weight_offset), stream_ptr())
@@ -448,7 +643,7 @@ def attention_tcgen05_error(head_dim: int) -> int:
 
 def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: int, n_prefill_tokens: int,
                           n_prefill_seqs: int, n_decode_seqs: int, max_kv_len: int, nq: int, nkv: int, head_dim: int,
-                          scale: float, window: int = 0, sinks=None) -> None:
+                          scale: float, window: int = 0, sinks=None, chunk: int = 0) -> None:
     """bfloat16 attention on the tensor cores.  Prompt portions go to the tcgen05 kernel, requests with
     one new token to the kernel that streams the cache with TMA, each where its shape is supported; what
     neither takes runs in the mma.sync kernel, whose single-token path shares a request's tiles between
@@ -468,7 +663,7 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
         attention_tcgen05.get(head_dim)[0](
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
-            nq, nkv, page_size, n_pages, int(window), float(scale), _ptr(sinks), stream_ptr())
+            nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(sinks), stream_ptr())
         if n_decode_seqs == 0:
             return
         n_prefill_tokens = n_prefill_seqs = 0
@@ -476,7 +671,7 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
         # single tokens: the kernel that streams the cache with TMA; what is left for the launch below are the
         # prompt portions (if the tcgen05 kernel did not take them)
         _attention_decode_tma(out, q, None, kv_pages, block_table, cu_q, kv_len, n_seqs, nq, nkv, head_dim, scale, window,
-                              sinks=sinks)
+                              sinks=sinks, chunk=chunk)
         if n_prefill_tokens == 0:
             return
         n_decode_seqs = 0
@@ -495,7 +690,7 @@ def attention_tensor_core(out, q, kv_pages, block_table, cu_q, kv_len, n_seqs: i
     library.LAUNCHES += 1
     launch(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kv_pages.data_ptr(), block_table.data_ptr(),
            block_table.stride(0), cu_q.data_ptr(), kv_len.data_ptr(), n_seqs, n_prefill_tokens, n_prefill_seqs,
-           n_decode_seqs, nq, nkv, page_size, n_pages, int(window), float(scale), _ptr(scratch_o), _ptr(scratch_ml),
+           n_decode_seqs, nq, nkv, page_size, n_pages, int(window), int(chunk), float(scale), _ptr(scratch_o), _ptr(scratch_ml),
            _ptr(counters), max_pieces, blocks, _ptr(sinks), stream_ptr())
 
 

@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import muvonex, qwen3  # noqa: F401
+from . import muvonex, nomudra, qwen3  # noqa: F401

@@ -1,4 +1,4 @@
-from . import (attention, block, delta_rule, embedding, feed_forward, norm, parallel_mixer, position,  # noqa: F401
+from . import (attention, block, delta_rule, embedding, feed_forward, mlstm, moe, norm, parallel_mixer, position,  # noqa: F401
                sink_attention, state_space)    # (importing registers the built-in parts)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block, BuildEnv, CacheView, CompositeNeed,
                    Embedding,

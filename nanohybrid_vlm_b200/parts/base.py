@@ -52,13 +52,14 @@ BLOCKS = Registry("block arrangement")
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every token (or of the last ``window`` tokens) in pages.  ``v_head_dim``: the size of a
-    value head where it differs from a key head's; a page row then has room for the larger of the two and each
-    kind uses its leading elements."""
+    """Keys and values of every token (or of the last ``window`` tokens, or of the current chunk of ``chunk``
+    positions) in pages.  ``v_head_dim``: the size of a value head where it differs from a key head's; a page row then
+    has room for the larger of the two and each kind uses its leading elements."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    chunk: int | None = None
 
     @property
     def row_dim(self) -> int:
@@ -142,8 +143,18 @@ class CacheView:
 class Pending:
     """Sub-block outputs that are not yet added to a float32 residual stream: the stream becomes
     stream + sum(coef * tensor) over ``terms`` ((tensor in the model's dtype, coef), ...), summed in 32-bit inside the
-    next norm.  Blocks that keep their stream in float32 hand this on in place of a hidden tensor."""
+    next norm.  Blocks that keep their stream in float32 hand this on in place of a hidden tensor.
+    ``post``: a norm that the (single) term still has to pass before it is added (blocks that norm a sub-block's
+    output as well as its input); the next norm applies it inside its own kernel where it can, else through
+    :meth:`settled`."""
     terms: tuple = ()
+    post: "Norm | None" = None
+
+    def settled(self) -> "Pending":
+        """The same sum with ``post`` applied by that norm's own ``forward`` (rounded to the model's type)."""
+        if self.post is None:
+            return self
+        return Pending(tuple((self.post.forward(t), c) for t, c in self.terms))
 
 
 class Mixer(Part):

@@ -48,5 +48,35 @@ class ParallelResidualBlock(Block):
         return Pending(tuple(terms)), residual
 
 
+class SandwichResidualBlock(Block):
+    """A norm before and after each sub-block: x <- x + post1(mixer(pre1(x))), then x <- x + post2(ffn(pre2(x))).  The
+    residual stream x is kept in float32.  A sub-block's output is handed on as a :class:`Pending` together with the
+    norm it still has to pass; the next norm in line (this layer's second pre-norm, the next layer's first, or the
+    model's last) applies that norm, adds the result in 32-bit and norms the sum, in one kernel where the norms allow it.
+    A layer may have no feed-forward (then also neither of its norms)."""
+    SLOTS = {"mixer": MIXERS, "mixer_norm": NORMS, "mixer_post_norm": NORMS, "ffn": FEED_FORWARDS, "ffn_norm": NORMS,
+             "ffn_post_norm": NORMS}
+    OPTIONAL = ("ffn", "ffn_norm", "ffn_post_norm")
+
+    def __init__(self, spec, parts):
+        super().__init__(spec, parts)
+        has = [name in parts for name in self.OPTIONAL]
+        if any(has) and not all(has):
+            raise ValueError("a feed-forward comes with both of its norms, or not at all")
+
+    def forward(self, hidden, residual, batch, cache):
+        if residual is None:
+            residual = hidden if hidden.dtype == torch.float32 else hidden.float()
+            hidden = Pending()
+        x = self.mixer_norm.forward_add(hidden, residual)
+        pending = Pending(((self.mixer.forward(x, batch, cache), 1.0),), post=self.mixer_post_norm)
+        ffn = self.parts.get("ffn")
+        if ffn is not None:
+            x = self.ffn_norm.forward_add(pending, residual)
+            pending = Pending(((ffn.forward(x, batch), 1.0),), post=self.ffn_post_norm)
+        return pending, residual
+
+
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+BLOCKS.register("sandwich_residual", SandwichResidualBlock)
 BLOCKS.register("parallel_residual", ParallelResidualBlock)

@@ -5,16 +5,18 @@ owns no tensor: it is given the embedding's table.
 
 Embedding parameters: ``vocab_size``, ``scale`` (a factor on the looked-up rows, default none), ``stream`` ("model":
 rows in the model's dtype; "float32": rows in 32-bit, for blocks that keep their residual stream in float32),
-``source`` (the checkpoint's name of the table, default "weight").  Head parameters: ``vocab_size``, ``tied``,
-``exact`` (True: the 32-bit sums of the product are the logits; False: rounded to the model's dtype first and then
-widened, as the reference's head does).
+``source`` (the checkpoint's name of the table, default "weight"), ``norm`` (a PartSpec of a norm that the looked-up
+rows pass before they become the stream, its tensors under the same prefix; the stream is then float32).  Head
+parameters: ``vocab_size``, ``tied``, ``exact`` (True: the 32-bit sums of the product are the logits; False: rounded to
+the model's dtype first and then widened, as the reference's head does), ``source`` (the checkpoint's name of an untied
+head's table; the part's own tensor then carries that name instead of "weight").
 """
 from __future__ import annotations
 
 import torch
 
 from ..kernels import ops
-from .base import EMBEDDINGS, HEADS, Embedding, Head
+from .base import EMBEDDINGS, HEADS, NORMS, Embedding, Head
 from .spec import ParamDecl, Source
 
 
@@ -29,11 +31,29 @@ class TokenEmbedding(Embedding):
             raise ValueError(f"an embedding's stream is 'model' or 'float32', not {self.stream!r}")
         if self.scale is not None and self.stream != "float32":
             raise ValueError("a scaled embedding writes a float32 stream")
+        norm = spec.get("norm")
+        self.norm = NORMS.get(norm.kind)(norm, env) if norm is not None else None
+        if self.norm is not None and (self.stream != "float32" or self.scale is not None):
+            raise ValueError("an embedding with a norm writes a float32 stream and has no scale")
 
     def params(self):
-        return [ParamDecl("weight", (self.vocab, self.env.hidden_size), sources=(Source(self.source, 0, self.vocab),))]
+        own = [ParamDecl("weight", (self.vocab, self.env.hidden_size), sources=(Source(self.source, 0, self.vocab),))]
+        return own + (self.norm.params() if self.norm is not None else [])
+
+    def bind(self, tensors):
+        self.w_weight = tensors["weight"]
+        if self.norm is not None:
+            self.norm.bind({name: t for name, t in tensors.items() if name != "weight"})
 
     def forward(self, token_ids, batch=None):
+        if self.norm is not None:
+            if hasattr(self.norm, "forward_embedding"):
+                return self.norm.forward_embedding(self.w_weight, token_ids)
+            rows = self.new(token_ids.numel(), self.env.hidden_size)
+            ops.embed(rows, self.w_weight, token_ids)
+            out = self.new(token_ids.numel(), self.env.hidden_size, dtype=torch.float32)
+            ops.to_f32(out, self.norm.forward(rows))
+            return out
         if self.stream == "float32":
             out = self.new(token_ids.numel(), self.env.hidden_size, dtype=torch.float32)
             ops.embed_scaled_f32(out, self.w_weight, token_ids, 1.0 if self.scale is None else float(self.scale))
@@ -49,9 +69,17 @@ class LMHead(Head):
         self.vocab = int(spec["vocab_size"])
         self.tied = bool(spec.get("tied", False))
         self.exact = bool(spec.get("exact", False))
+        self.source = spec.get("source")
 
     def params(self):
-        return [] if self.tied else [ParamDecl("weight", (self.vocab, self.env.hidden_size))]
+        if self.tied:
+            return []
+        if self.source is None:
+            return [ParamDecl("weight", (self.vocab, self.env.hidden_size))]
+        return [ParamDecl(self.source, (self.vocab, self.env.hidden_size), sources=(Source(self.source, 0, self.vocab),))]
+
+    def bind(self, tensors):
+        (self.w_weight,) = tensors.values()
 
     def tie(self, embedding) -> None:
         self.w_weight = embedding.w_weight

@@ -1,4 +1,4 @@
-"""RMSNorm with the residual add fused in (nanovllm/layers/layernorm.py:5-50).
+"""Norms: RMSNorm with the residual add fused in (nanovllm/layers/layernorm.py:5-50), and Dynamic Tanh.
 
 Parameters: ``width``, ``eps``, ``weight_offset`` (0 for ``x * w``; 1 for the ``x * (1 + w)``
 convention some models store), ``source`` (the checkpoint's name of the weight, default "weight").
@@ -7,6 +7,8 @@ Over a residual stream kept in float32 (``forward_add`` / ``forward_add_rows`` g
 are added in 32-bit, the statistics and the product with the weight are 32-bit, and the result is rounded once.
 """
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 from .base import NORMS, Norm, Pending
@@ -32,6 +34,7 @@ class RMSNorm(Norm):
 
     def forward_add(self, x, residual):
         if isinstance(x, Pending):
+            x = x.settled()
             out = self.new(*residual.shape)
             ops.rmsnorm_stream(out, residual, self.w_weight, self.eps, addends=x.terms, weight_offset=self.weight_offset)
             return out
@@ -41,6 +44,7 @@ class RMSNorm(Norm):
 
     def forward_add_rows(self, x, residual, rows):
         if isinstance(x, Pending):
+            x = x.settled()
             out = self.new(rows.numel(), residual.shape[-1])
             ops.rmsnorm_stream(out, residual, self.w_weight, self.eps, addends=x.terms, rows=rows, write_stream=False,
                                weight_offset=self.weight_offset)
@@ -51,4 +55,64 @@ class RMSNorm(Norm):
         return out
 
 
+class DynamicTanh(Norm):
+    """y = tanh(alpha * x) * w + b: a norm without statistics (a learned scalar ``alpha``, learned vectors ``w``, ``b``).
+
+    Parameters: ``width``, ``source`` (the checkpoint's name of the weight; the bias is ``<source>.b`` and alpha, stored
+    without a shape, ``<source>.alpha``; the part's own tensors carry the same names, so several norms can share a
+    prefix).  Computed in 32-bit.  Over a float32 residual stream (``forward_add`` / ``forward_add_rows`` given a
+    :class:`Pending`) the kernel also adds the sub-block output that is pending, after the Dynamic Tanh norm that this
+    output still has to pass (``Pending.post``), all in 32-bit: one launch between two sub-blocks."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.width = int(spec["width"])
+        self.source = spec.get("source", "weight")
+
+    def params(self):
+        s = self.source
+        return [ParamDecl(s, (self.width,), init="norm", sources=(Source(s, 0, self.width),)),
+                ParamDecl(s + ".b", (self.width,), init="zeros_noise", sources=(Source(s + ".b", 0, self.width),)),
+                ParamDecl(s + ".alpha", (1,), init="dyntanh_alpha", sources=(Source(s + ".alpha", 0, 1, squeeze=True),))]
+
+    def bind(self, tensors):
+        s = self.source
+        self.w_weight, self.w_bias, self.w_alpha = tensors[s], tensors[s + ".b"], tensors[s + ".alpha"]
+
+    @property
+    def triple(self):
+        return self.w_alpha, self.w_weight, self.w_bias
+
+    def forward(self, x):
+        out = self.new(*x.shape)
+        ops.dyntanh(out, x, *self.triple)
+        return out
+
+    def forward_embedding(self, table, token_ids):
+        """The looked-up rows of ``table`` through this norm, as a float32 stream [T, width]."""
+        out = self.new(token_ids.numel(), self.width, dtype=torch.float32)
+        ops.embed_dyntanh(out, table, token_ids, *self.triple)
+        return out
+
+    def _stream(self, x, residual, rows, n_rows):
+        if not isinstance(x, Pending) or residual.dtype != torch.float32:
+            raise TypeError("the Dynamic Tanh norm adds into a float32 residual stream: it takes a Pending")
+        if x.post is not None and not isinstance(x.post, DynamicTanh):
+            x = x.settled()
+        if len(x.terms) > 1 or any(c != 1.0 for _, c in x.terms):
+            raise ValueError("the Dynamic Tanh norm adds at most one pending sub-block output, with factor 1")
+        out = self.new(n_rows, self.width)
+        addend = x.terms[0][0] if x.terms else None
+        ops.dyntanh_stream(out, residual, self.triple, addend, x.post.triple if x.post is not None else None, rows=rows,
+                           write_stream=rows is None)
+        return out
+
+    def forward_add(self, x, residual):
+        return self._stream(x, residual, None, residual.shape[0])
+
+    def forward_add_rows(self, x, residual, rows):
+        return self._stream(x, residual, rows, rows.numel())
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("dyntanh", DynamicTanh)

@@ -3,7 +3,7 @@ and a seed, and the same weights made directly on the device for models too larg
 write out.
 
 Matrices and embeddings are N(0, 0.02); norm weights are 1 + N(0, 0.01) (or N(0, 0.01)
-for norms stored as an offset from one).  Each checkpoint tensor has its own generator
+for norms stored as an offset from one); parts may name further kinds (``INITS``).  Each checkpoint tensor has its own generator
 seeded from (seed, tensor name), so a tensor's values do not depend on the others.
 """
 from __future__ import annotations
@@ -36,6 +36,8 @@ INITS = {
     "normal": _normal(0.02),
     "norm": _normal(0.01, 1.0),
     "zeros_noise": _normal(0.01),
+    "dyntanh_alpha": _normal(0.05, 0.5),        # the scalar of a Dynamic Tanh norm
+    "gate_bias": _normal(1.0),                  # biases of recurrent gates: spread, so that decays differ
     "zeros": lambda shape, gen, device: torch.zeros(shape, dtype=torch.float32, device=device),
 }
 
