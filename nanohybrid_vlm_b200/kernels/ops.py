@@ -370,17 +370,39 @@ def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: 
          sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, stream_ptr())
 
 
+MOE_ON_TENSOR_CORES = True      # tests switch it off to compare with the CUDA-core products at the same shapes
+MOE_TILE = 0                    # rows per tile of the tensor-core products: 0 chooses by the step; tests set 16 or 64
+
+
 def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
     """Every chosen expert's output for every token: orders the slots of ids [T, top] by expert and runs the experts' two
-    products over that order.  Returns (y [rows, width], one row per slot that chose a real expert, and slot_pos
-    [T * top] int32, the row of each slot or -1)."""
+    products over that order: bfloat16 with sizes in steps of 8 on the tensor cores (tiles of 64 rows where an expert
+    sees many rows, of 16 where it sees few and the products stream the weights), everything else on the CUDA cores.
+    Returns (y [rows, width], one row per slot that chose a real expert, and slot_pos [T * top] int32, the row of each
+    slot or -1)."""
     E, ff, width = gate.shape
     top = ids.shape[1]
-    sorted_slots, slot_pos, tile_expert = moe_align(ids, E, MOE_TILE_SIMT)
+    mma = MOE_ON_TENSOR_CORES and x.dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0
+    tile = MOE_TILE_SIMT
+    if mma:
+        tile = MOE_TILE or (64 if ids.numel() >= 24 * E else 16)
+    sorted_slots, slot_pos, tile_expert = moe_align(ids, E, tile)
     rows = sorted_slots.numel()
     act = torch.empty(rows, ff, dtype=x.dtype, device=x.device)
     y = torch.empty(rows, width, dtype=x.dtype, device=x.device)
-    moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top, limit, alpha)
+    if not mma:
+        moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top, limit, alpha)
+        return y, slot_pos
+    _need_cuda(x, gate, up, down, ids)
+    for name, t in (("x", x), ("gate", gate), ("up", up), ("down", down)):
+        _contig(name, t)
+    assert up.shape == gate.shape and down.shape == (E, width, ff) and x.shape[1] == width
+    assert gate.dtype == up.dtype == down.dtype == torch.bfloat16
+    tiles = tile_expert.numel()
+    call("nhv_moe_gemm_mma", tile, 1, act.data_ptr(), x.data_ptr(), width, gate.data_ptr(), up.data_ptr(),
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), stream_ptr())
+    call("nhv_moe_gemm_mma", tile, 0, y.data_ptr(), act.data_ptr(), ff, down.data_ptr(), None,
+         sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, stream_ptr())
     return y, slot_pos
 
 
