@@ -4,6 +4,7 @@
     python bench.py --workload 0.6b|32b      the baseline's other two workloads, through the Python entry point
     python bench.py --breakdown              where a decode step's and a prefill's time goes, by kind of kernel
     python bench.py --designs                Muvonex beside a Qwen3 of equal size (prefill, decode, time by kind of kernel)
+    python bench.py --designs nomudra        Nomudra beside a Muvonex of equal active size, the same way
 
 The default run has the layer sizes of the Qwen3-8B-shaped configuration (36 layers, width 4096,
 32/8 heads of 128, feed-forward 12288, vocabulary 151936), bfloat16, random weights, batch 8,
@@ -664,6 +665,20 @@ def muvonex_config(width: int, heads: int, ff: int, layers: int) -> dict:
                 residual_mult=1.0, layers=[par if i % 4 == 3 else delta for i in range(layers)], dtype="bfloat16")
 
 
+def nomudra_config(width: int, heads: int, ff: int, layers: int) -> dict:
+    """Attention in chunks of 4,096 and mLSTM layers in turn, each with a mixture of 16 experts and 2 identity experts of
+    which a token uses 4, and a shared expert: the experts a token uses and the shared one are together as wide as the
+    dense feed-forward ``ff`` of the other designs (4 * 2/11 + 3/11 of it)."""
+    moe = dict(kind="moe", router=dict(experts=16, identity=2, top=4, groups=dict(count=3, keep=2)),
+               expert=dict(ff=ff * 2 // 11, limit=7.0), shared=dict(ff=ff * 3 // 11, limit=7.0))
+    attention = dict(type="attention", mlp=moe, mixer=dict(
+        heads=heads, kv_heads=max(heads // 4, 1), dim=128, vdim=128, scale=128 ** -0.5, rot=dict(base=500000.0, dims=64),
+        mask=dict(size=4096)))
+    mlstm = dict(type="mlstm", mlp=moe, mixer=dict(heads=heads // 2, dim=128, vdim=256, gate_cap=15.0))
+    return dict(architecture="Nomudra", vocab=DESIGN_VOCAB, width=width, norm=dict(eps=1e-6),
+                layers=[attention if i % 2 == 0 else mlstm for i in range(layers)], dtype="bfloat16")
+
+
 def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weights: float) -> dict:
     """A Qwen3 of this width whose layers hold as many weights as ``layer_weights`` (the feed-forward takes up the
     difference, rounded to 256)."""
@@ -675,8 +690,10 @@ def qwen3_config_of_equal_size(width: int, heads: int, layers: int, layer_weight
 
 
 def bench_designs(args) -> dict:
-    """Prefill and decode throughput of Muvonex beside a Qwen3 of equal size, and the time of each kind of kernel in
-    a prefill step (CUDA events around every launch of an eager run) with its share of the measured roofline."""
+    """Prefill and decode throughput of Muvonex beside a Qwen3 of equal size (``--designs``), or of Nomudra beside a
+    Muvonex whose layers hold as many weights as a Nomudra token uses (``--designs nomudra``), and the time of each kind
+    of kernel in a prefill step (CUDA events around every launch of an eager run) with its share of the measured
+    roofline."""
     import torch
 
     from nanohybrid_vlm_b200 import LLM
@@ -690,10 +707,24 @@ def bench_designs(args) -> dict:
              "qk_norm_rope_store": "rope_store", "rope_norm_store": "rope_store", "attention": "attention",
              "attention_sink": "attention", "attention_decode_fused": "attention", "silu_mul": "act_mul",
              "gelu_tanh_mul": "act_mul", "embed": "embed", "embed_scaled_f32": "embed", "short_conv_silu": "short_conv",
-             "delta_rule": "delta_rule", "ssd_scan": "ssd_scan", "gated_rmsnorm": "gated_norm", "sample": "sample"}
+             "delta_rule": "delta_rule", "ssd_scan": "ssd_scan", "gated_rmsnorm": "gated_norm", "sample": "sample",
+             "dyntanh": "norm", "dyntanh_stream": "norm", "embed_dyntanh": "embed", "mlstm_scan": "mlstm_scan",
+             "sigmoid_mul": "act_mul", "add_row_bias": "act_mul", "clamped_glu": "act_mul", "moe_route": "router",
+             "moe_experts": "experts", "moe_combine": "experts_sum"}
     kinds = {k: v for k, v in kinds.items() if hasattr(ops, k)}
     stock = {name: getattr(ops, name) for name in kinds}
     gen = torch.Generator().manual_seed(SEED)
+
+    def run_one_weights(cfg: dict) -> float:
+        """Weights in the matrices of a configuration's layers (no device needed: the table of its tensors)."""
+        from nanohybrid_vlm_b200.config.registry import ARCHITECTURES
+        from nanohybrid_vlm_b200.engine.model import CausalLM
+        from dataclasses import replace
+        entry = ARCHITECTURES.resolve(cfg)
+        spec = replace(entry.build_spec(entry.parse_config(cfg)), max_position=16)      # no long tables for a count
+        table = CausalLM(spec, torch.bfloat16, "cpu").param_table()
+        return float(sum(bp.decl.shape[0] * bp.decl.shape[1] for bp in table if len(bp.decl.shape) == 2)
+                     - DESIGN_VOCAB * cfg["width"])
 
     def run_one(cfg: dict, vocab: int) -> dict:
         with tempfile.TemporaryDirectory() as d:
@@ -704,6 +735,12 @@ def bench_designs(args) -> dict:
                       enforce_eager=args.eager)
         runner = llm.model_runner
         weights = sum(bp.decl.shape[0] * bp.decl.shape[1] for bp in runner.model.param_table() if len(bp.decl.shape) == 2)
+        # stacks of experts [E, rows, columns]: a token uses `top` of the E (fewer where it chooses identity experts)
+        stacks = [bp.decl.shape for bp in runner.model.param_table() if len(bp.decl.shape) == 3]
+        expert_weights = sum(e * r * c for e, r, c in stacks)
+        tops = [dict(lay.ffn.spec.items) for lay in runner.model.spec.layers if "ffn" in dict(lay.parts)
+                and lay.ffn.spec.kind == "routed_moe"]
+        used = sum(3 * t["top"] * t["intermediate_size"] * cfg.get("width", 0) for t in tops)
         prompt = torch.randint(0, vocab, (T,), generator=gen).tolist()
         events, depth = [], [0]
 
@@ -750,12 +787,15 @@ def bench_designs(args) -> dict:
         by_kind = {}
         for kind, a, b in events:
             by_kind[kind] = by_kind.get(kind, 0.0) + a.elapsed_time(b) * 1e3 / reps
-        out = {"weights_m": round(weights / 1e6, 1), "prefill_ms": round(prefill_ms, 3),
+        out = {"weights_m": round((weights + expert_weights) / 1e6, 1), "weights_a_token_uses_m": round((weights + used) / 1e6, 1),
+               "prefill_ms": round(prefill_ms, 3),
                "prefill_tok_s": round(T / prefill_ms * 1e3),
                "prefill_us_by_kind": {k: round(v, 1) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])}}
         gemm_flops = 2.0 * T * (weights - vocab * cfg.get("width", cfg.get("hidden_size")))
         if "gemm" in by_kind:
             out["gemm_frac_of_measured_bf16"] = round(gemm_flops / (by_kind["gemm"] * 1e-6) / (pk["bf16_tflops"] * 1e12), 3)
+        if "experts" in by_kind:     # an upper bound of the work: every choice counted as a real expert
+            out["experts_frac_of_measured_bf16"] = round(2.0 * T * used / (by_kind["experts"] * 1e-6) / (pk["bf16_tflops"] * 1e12), 3)
         for batch in (8, 64):
             ids = [f"d{batch}_{i}" for i in range(batch)]
             lens = {}
@@ -783,7 +823,9 @@ def bench_designs(args) -> dict:
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / steps
             item = 2
-            read = weights * item + sum(runner.layout.page_bytes(page, torch.bfloat16)) * batch * (ctx // page) \
+            # of a stack of E experts a step reads those that some token chose: at most batch * top of them
+            hit = sum(min(e, batch * t["top"]) * r * c for (e, r, c), t in zip(stacks, [t for t in tops for _ in range(3)]))
+            read = (weights + hit) * item + sum(runner.layout.page_bytes(page, torch.bfloat16)) * batch * (ctx // page) \
                 + runner.layout.state_bytes_per_slot(torch.bfloat16) * batch * 2
             out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 3), "tok_s": round(batch / ms * 1e3),
                                        "hbm_frac_of_measured": round(read / (ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)}
@@ -796,6 +838,15 @@ def bench_designs(args) -> dict:
     results = {}
     for name in ([args.design_size] if args.design_size != "all" else list(DESIGN_SIZES)):
         sz = DESIGN_SIZES[name]
+        if args.designs == "nomudra":
+            n = run_one(nomudra_config(sz["width"], sz["heads"], sz["ff"], layers), DESIGN_VOCAB)
+            # a Muvonex whose dense feed-forward makes up for the difference in the mixers' weights
+            per_layer = (n["weights_a_token_uses_m"] * 1e6 - DESIGN_VOCAB * sz["width"]) / layers
+            probe = muvonex_config(sz["width"], sz["heads"], sz["ff"], layers)
+            m0 = run_one_weights(probe)
+            ff = max(256, int(round((sz["ff"] + (per_layer - m0 / layers) / (3 * sz["width"])) / 256)) * 256)
+            results[name] = {"nomudra": n, "muvonex": run_one(muvonex_config(sz["width"], sz["heads"], ff, layers), DESIGN_VOCAB)}
+            continue
         mcfg = muvonex_config(sz["width"], sz["heads"], sz["ff"], layers)
         m = run_one(mcfg, DESIGN_VOCAB)
         layer_weights = (m["weights_m"] * 1e6 - DESIGN_VOCAB * sz["width"]) / layers
@@ -827,8 +878,9 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=0, help="fewer requests than the workload names (trying it out)")
     ap.add_argument("--breakdown", action="store_true",
                     help="time by kind of kernel in an eager run with --layers layers (default 2); prints one JSON line")
-    ap.add_argument("--designs", action="store_true",
-                    help="Muvonex beside a Qwen3 of equal size: prefill and decode throughput at a few layer sizes; one JSON line")
+    ap.add_argument("--designs", nargs="?", const="muvonex", default=None, choices=["muvonex", "nomudra"],
+                    help="two designs side by side, prefill and decode throughput at a few layer sizes, one JSON line: "
+                         "Muvonex beside a Qwen3 of equal size (the default), or Nomudra beside a Muvonex of equal active size")
     ap.add_argument("--design-size", default="all", choices=["all", *DESIGN_SIZES], help="one size of --designs")
     args = ap.parse_args()
     if args.gpus != 1:

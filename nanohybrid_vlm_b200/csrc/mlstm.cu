@@ -22,16 +22,39 @@
 
 constexpr int ML_COLS = 16;
 constexpr int ML_PARTS = 8;
-constexpr int ML_CHUNK = 16;
+constexpr int ML_CHUNK = 32;
 
 __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T, int R>
+// Eight consecutive elements as floats (p on a 16-byte boundary).
+__device__ __forceinline__ void ml_load8(float (&o)[8], const float* p) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void ml_load8(float (&o)[8], const __nv_bfloat16* p) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+
+// Which row of its column a lane's r-th register holds.  VEC (d in steps of 32): groups of four consecutive rows, so
+// that one 16-byte read of k and one of q from shared memory serve four rows; else rows ML_PARTS apart.
+template <bool VEC> __device__ __forceinline__ int ml_row(int part, int r) {
+  return VEC ? ((r >> 2) * (4 * ML_PARTS) + part * 4 + (r & 3)) : (part + r * ML_PARTS);
+}
+
+// VEC also reads the tokens' rows of proj eight elements at a time (the host checks sizes and alignment).
+template <typename T, int R, bool VEC>
 __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
     float* __restrict__ y, const T* __restrict__ proj, int proj_stride, const float* __restrict__ gates, int gate_stride,
     const float* __restrict__ gate_bias, float cap, float* __restrict__ state, long state_stride,
     const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ slots, int H, int d, int dv) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_prologue();
   const int s = blockIdx.x, h = blockIdx.y, cb = blockIdx.z, col0 = cb * ML_COLS;
   const int first = cu_q[s], n = cu_q[s + 1] - first;
@@ -59,7 +82,7 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
   float S[R], Nn[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = part + r * ML_PARTS;
+    const int i = ml_row<VEC>(part, r);
     S[r] = (live && !fresh && i < d) ? st[i] : 0.f;
     Nn[r] = (!fresh && i < d) ? nm[i] : 0.f;
   }
@@ -70,11 +93,28 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
   for (int c0 = 0; c0 < n; c0 += ML_CHUNK) {
     const int cn = min(ML_CHUNK, n - c0);
     __syncthreads();
-    for (int i = tid; i < cn * d; i += blockDim.x) {
-      const int tt = i / d, c = i - tt * d;
-      const T* row = proj + (size_t)(first + c0 + tt) * proj_stride;
-      qs[i] = to_f32<T>(row[q_off + c]) * qscale;
-      ks[i] = to_f32<T>(row[k_off + c]);
+    if (VEC) {
+      const int d8 = d >> 3;
+      for (int i = tid; i < cn * d8; i += blockDim.x) {
+        const int tt = i / d8, c = (i - tt * d8) * 8;
+        const T* row = proj + (size_t)(first + c0 + tt) * proj_stride;
+        float q8[8], k8[8];
+        ml_load8(q8, row + q_off + c);
+        ml_load8(k8, row + k_off + c);
+        float* qd = qs + tt * d + c;
+        float* kd = ks + tt * d + c;
+        *reinterpret_cast<float4*>(qd) = make_float4(q8[0] * qscale, q8[1] * qscale, q8[2] * qscale, q8[3] * qscale);
+        *reinterpret_cast<float4*>(qd + 4) = make_float4(q8[4] * qscale, q8[5] * qscale, q8[6] * qscale, q8[7] * qscale);
+        *reinterpret_cast<float4*>(kd) = make_float4(k8[0], k8[1], k8[2], k8[3]);
+        *reinterpret_cast<float4*>(kd + 4) = make_float4(k8[4], k8[5], k8[6], k8[7]);
+      }
+    } else {
+      for (int i = tid; i < cn * d; i += blockDim.x) {
+        const int tt = i / d, c = i - tt * d;
+        const T* row = proj + (size_t)(first + c0 + tt) * proj_stride;
+        qs[i] = to_f32<T>(row[q_off + c]) * qscale;
+        ks[i] = to_f32<T>(row[k_off + c]);
+      }
     }
     for (int i = tid; i < cn * ncol; i += blockDim.x) {
       const int tt = i / ncol, c = i - tt * ncol;
@@ -110,35 +150,57 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
       gm[tid] = expf(-m_new);
     }
     __syncthreads();
+    // Only S and n are carried from token to token (one multiply-add each); the sums over rows, their shuffles and the
+    // division of one token overlap with the next tokens' updates once the loop is unrolled.
+#pragma unroll 4
     for (int tt = 0; tt < cn; ++tt) {
       const float a = ga[tt], b = gb[tt];
       const float bv = live ? b * vs[tt * ML_COLS + cl] : 0.f;
       const float* kt = ks + tt * d;
       const float* qt = qs + tt * d;
-      float acc = 0.f, accn = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, accn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (VEC) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int i = part + r * ML_PARTS;
-        if (i < d) {
-          const float kk = kt[i], qq = qt[i];
-          S[r] = fmaf(a, S[r], bv * kk);
-          Nn[r] = fmaf(a, Nn[r], b * kk);
-          acc = fmaf(S[r], qq, acc);
-          accn = fmaf(Nn[r], qq, accn);
+        for (int j = 0; j < R / 4; ++j) {
+          const int i0 = j * (4 * ML_PARTS) + part * 4;
+          if (i0 < d) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kt + i0), q4 = *reinterpret_cast<const float4*>(qt + i0);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              S[4 * j + e] = fmaf(a, S[4 * j + e], bv * kk[e]);
+              Nn[4 * j + e] = fmaf(a, Nn[4 * j + e], b * kk[e]);
+              acc[e] = fmaf(S[4 * j + e], qq[e], acc[e]);
+              accn[e] = fmaf(Nn[4 * j + e], qq[e], accn[e]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int i = part + r * ML_PARTS;
+          if (i < d) {
+            const float kk = kt[i], qq = qt[i];
+            S[r] = fmaf(a, S[r], bv * kk);
+            Nn[r] = fmaf(a, Nn[r], b * kk);
+            acc[r & 3] = fmaf(S[r], qq, acc[r & 3]);
+            accn[r & 3] = fmaf(Nn[r], qq, accn[r & 3]);
+          }
         }
       }
+      float so = (acc[0] + acc[1]) + (acc[2] + acc[3]), sn = (accn[0] + accn[1]) + (accn[2] + accn[3]);
 #pragma unroll
       for (int o = 1; o < ML_PARTS; o <<= 1) {
-        acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        accn += __shfl_xor_sync(0xffffffffu, accn, o);
+        so += __shfl_xor_sync(0xffffffffu, so, o);
+        sn += __shfl_xor_sync(0xffffffffu, sn, o);
       }
       if (live && part == 0)
-        y[(size_t)(first + c0 + tt) * inner + h * dv + col] = acc / (fmaxf(fabsf(accn), gm[tt]) + 1e-6f);
+        y[(size_t)(first + c0 + tt) * inner + h * dv + col] = so / (fmaxf(fabsf(sn), gm[tt]) + 1e-6f);
     }
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = part + r * ML_PARTS;
+    const int i = ml_row<VEC>(part, r);
     if (i < d) {
       if (live) st[i] = S[r];
       if (cl == 0) nm[i] = Nn[r];
@@ -166,21 +228,25 @@ NHV_API int nhv_mlstm_scan(int dtype, float* y, const void* proj, int proj_strid
   const int rows = (d + ML_PARTS - 1) / ML_PARTS;
   const size_t smem = ((size_t)ML_CHUNK * (2 * d + ML_COLS) + 3 * ML_CHUNK + 1) * sizeof(float);
   dim3 grid(n_seqs, H, (dv + ML_COLS - 1) / ML_COLS);
-#define SCAN(T, R)                                                                                                  \
+  // rows in groups of four and tokens read eight elements at a time, where sizes and alignment allow it
+  const size_t item = dtype == NHV_F32 ? 4 : 2;
+  const bool vec = d % (4 * ML_PARTS) == 0 && dv % 8 == 0 && proj_stride % 8 == 0 && ((uintptr_t)proj % 16) == 0 &&
+                   ((size_t)H * d * item) % 16 == 0;
+#define SCAN(T, R, V)                                                                                               \
   do {                                                                                                              \
     if (smem > 48 * 1024)                                                                                           \
-      NHV_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
-               "mlstm_scan");                                                                                       \
-    nhv_launch(mlstm_scan_kernel<T, R>, grid, ML_COLS * ML_PARTS, smem, stream, y, (const T*)proj, proj_stride, gates, \
-               gate_stride, gate_bias, cap, state, state_stride, cu_q, q_start, slots, H, d, dv);                   \
+      NHV_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, R, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                    (int)smem), "mlstm_scan");                                                      \
+    nhv_launch(mlstm_scan_kernel<T, R, V>, grid, ML_COLS * ML_PARTS, smem, stream, y, (const T*)proj, proj_stride,  \
+               gates, gate_stride, gate_bias, cap, state, state_stride, cu_q, q_start, slots, H, d, dv);            \
   } while (0)
-#define LAUNCH(T)                          \
-  do {                                     \
-    if (rows <= 4) SCAN(T, 4);             \
-    else if (rows <= 8) SCAN(T, 8);        \
-    else if (rows <= 16) SCAN(T, 16);      \
-    else if (rows <= 32) SCAN(T, 32);      \
-    else SCAN(T, 64);                      \
+#define LAUNCH(T)                                                   \
+  do {                                                              \
+    if (rows <= 4) { if (vec) SCAN(T, 4, true); else SCAN(T, 4, false); }            \
+    else if (rows <= 8) { if (vec) SCAN(T, 8, true); else SCAN(T, 8, false); }       \
+    else if (rows <= 16) { if (vec) SCAN(T, 16, true); else SCAN(T, 16, false); }    \
+    else if (rows <= 32) { if (vec) SCAN(T, 32, true); else SCAN(T, 32, false); }    \
+    else { if (vec) SCAN(T, 64, true); else SCAN(T, 64, false); }                    \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);

@@ -281,7 +281,36 @@ NHV_API int nhv_moe_gemm_simt(int dtype, int first, void* out, const void* A, in
 }
 
 // ---------------------------------------------------------------- the weighted sum
-template <typename T>
+// Eight consecutive elements (16 bytes of bfloat16, 32 of float) as floats, and back.
+__device__ __forceinline__ void mc_load8(float (&o)[8], const float* p) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void mc_load8(float (&o)[8], const __nv_bfloat16* p) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    o[2 * i] = f.x;
+    o[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void mc_store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void mc_store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// VEC: eight columns per thread and step (width in steps of 8, rows on 16-byte boundaries); the sums run in the same
+// order either way.
+template <typename T, bool VEC>
 __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y, const T* __restrict__ x,
                                    const T* __restrict__ shared, const float* __restrict__ shared_gate, int gate_stride,
                                    const int* __restrict__ ids, const float* __restrict__ weights,
@@ -299,16 +328,40 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
   __syncthreads();
   float sg = 0.f;
   if (shared) sg = shared_gate ? 1.0f / (1.0f + expf(-shared_gate[(size_t)t * gate_stride])) : 1.0f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float acc = 0.f;
-    const float xv = to_f32<T>(x[(size_t)t * width + c]);
-    for (int k = 0; k < top; ++k) {
-      const int p = pos[k];
-      if (p >= 0) acc = fmaf(w[k], to_f32<T>(y[(size_t)p * width + c]), acc);
-      else if (p == -2) acc = fmaf(w[k], xv, acc);
+  if constexpr (VEC) {
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, xv[8], v[8];
+      mc_load8(xv, x + (size_t)t * width + c);
+      for (int k = 0; k < top; ++k) {
+        const int p = pos[k];
+        if (p >= 0) {
+          mc_load8(v, y + (size_t)p * width + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[k], v[i], acc[i]);
+        } else if (p == -2) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[k], xv[i], acc[i]);
+        }
+      }
+      if (shared) {
+        mc_load8(v, shared + (size_t)t * width + c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(sg, v[i], acc[i]);
+      }
+      mc_store8(out + (size_t)t * width + c, acc);
     }
-    if (shared) acc = fmaf(sg, to_f32<T>(shared[(size_t)t * width + c]), acc);
-    out[(size_t)t * width + c] = from_f32<T>(acc);
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float acc = 0.f;
+      const float xv = to_f32<T>(x[(size_t)t * width + c]);
+      for (int k = 0; k < top; ++k) {
+        const int p = pos[k];
+        if (p >= 0) acc = fmaf(w[k], to_f32<T>(y[(size_t)p * width + c]), acc);
+        else if (p == -2) acc = fmaf(w[k], xv, acc);
+      }
+      if (shared) acc = fmaf(sg, to_f32<T>(shared[(size_t)t * width + c]), acc);
+      out[(size_t)t * width + c] = from_f32<T>(acc);
+    }
   }
 }
 
@@ -317,13 +370,15 @@ NHV_API int nhv_moe_combine(int dtype, void* out, const void* y, const void* x, 
                             int top, int E, int width, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   NHV_REQUIRE(top > 0 && top <= 1024 && width > 0, "moe_combine: bad sizes");
-  const int threads = width >= 1024 ? 256 : 128;
+  const bool vec = width % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)x % 16) == 0 &&
+                   ((uintptr_t)shared % 16) == 0;
+  const int threads = vec ? (width >= 2048 ? 256 : 128) : (width >= 1024 ? 256 : 128);
   const size_t smem = (size_t)top * 8;
-#define GO(T)                                                                                                    \
-  nhv_launch(moe_combine_kernel<T>, n_tokens, threads, smem, stream, (T*)out, (const T*)y, (const T*)x, (const T*)shared, \
+#define GO(T, V)                                                                                                 \
+  nhv_launch(moe_combine_kernel<T, V>, n_tokens, threads, smem, stream, (T*)out, (const T*)y, (const T*)x, (const T*)shared, \
              shared_gate, gate_stride, ids, weights, slot_pos, top, E, width)
-  if (dtype == NHV_F32) GO(float);
-  else if (dtype == NHV_BF16) GO(__nv_bfloat16);
+  if (dtype == NHV_F32) { if (vec) GO(float, true); else GO(float, false); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false); }
   else NHV_REQUIRE(false, "moe_combine: unknown dtype %d", dtype);
 #undef GO
   NHV_CHECK_LAUNCH("moe_combine");

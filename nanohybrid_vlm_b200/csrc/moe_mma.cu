@@ -8,9 +8,10 @@
 //           same (row, column) in the same thread, so the unit is applied without leaving the registers;
 //   second: y[row, c] = act[row] . Wd[e][c]                                          128 columns.
 // A rows are gathered by token on their way into shared memory.  Operands travel by cp.async in a ring of three
-// stages of 64 columns of K; a row's sum over K runs in the same order wherever the row stands, so results do not
-// depend on the ordering.  BM is 16 where experts see few rows (decoding: the kernel streams each expert's weights
-// once) and 64 for prompts.
+// stages of 32 columns of K (small stages: several blocks fit an SM, and the tensor pipe needs many warps to stay
+// busy); a row's sum over K runs in the same order wherever the row stands, so results do not depend on the
+// ordering.  BM is 16 where experts see few rows (decoding: the kernel streams each expert's weights once), 64 or
+// 128 (eight warps, each panel of weights read for twice the rows) for prompts.
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -18,11 +19,10 @@
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int MM_BK = 64;
+constexpr int MM_BK = 32;
 constexpr int MM_LDS = MM_BK + 8;       // a row of a stage in shared memory, padded against bank conflicts
 constexpr int MM_STAGES = 3;
 constexpr int MM_BROWS = 128;
-constexpr int MM_THREADS = 128;
 
 __device__ __forceinline__ void mm_cp_async16(void* smem, const void* gmem, int bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem),
@@ -49,12 +49,17 @@ __device__ __forceinline__ float mm_glu(float g, float u, float limit, float alp
 }
 __device__ __forceinline__ float mm_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+template <int BM> struct MmShape {
+  static constexpr int WM = BM >= 64 ? 64 : 16;        // rows per warp
+  static constexpr int THREADS = (BM / WM) * 4 * 32;   // warps: BM / WM along the rows x 4 along the columns
+};
+
 template <int BM, bool FIRST>
-__global__ void __launch_bounds__(MM_THREADS) moe_gemm_mma_kernel(
+__global__ void __launch_bounds__(MmShape<BM>::THREADS) moe_gemm_mma_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ A, int lda, const bf16* __restrict__ W0, const bf16* __restrict__ W1,
     const int* __restrict__ sorted_slots, const int* __restrict__ tile_expert, int top, int N, int K, float limit,
     float alpha) {
-  constexpr int MT = BM / 16;
+  constexpr int MT = MmShape<BM>::WM / 16, MM_THREADS = MmShape<BM>::THREADS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* As = reinterpret_cast<bf16*>(smem_raw);              // [STAGES][BM][LDS]
   bf16* Bs = As + MM_STAGES * BM * MM_LDS;                   // [STAGES][BROWS][LDS]
@@ -64,7 +69,8 @@ __global__ void __launch_bounds__(MM_THREADS) moe_gemm_mma_kernel(
   const int e = tile_expert[tile];
   if (e < 0) return;
   const int n0 = blockIdx.y * (FIRST ? 64 : 128);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = (tid >> 5) & 3, row0 = (tid >> 7) * MmShape<BM>::WM;       // column quarter, first row of the warp
   if (tid < BM) {
     const int row = tile * BM + tid;
     const int slot = sorted_slots[row];
@@ -77,14 +83,15 @@ __global__ void __launch_bounds__(MM_THREADS) moe_gemm_mma_kernel(
 
   auto load_stage = [&](int stage, int kt) {
     const int k0 = kt * MM_BK;
-    for (int i = tid; i < BM * 8; i += MM_THREADS) {
-      const int r = i >> 3, c = i & 7, k = k0 + c * 8;
+    constexpr int CH = MM_BK / 8;                              // 16-byte pieces of a row of a stage
+    for (int i = tid; i < BM * CH; i += MM_THREADS) {
+      const int r = i / CH, c = i % CH, k = k0 + c * 8;
       const int src = arow[r];
       const bool ok = src >= 0 && k < K;
       mm_cp_async16(As + ((size_t)stage * BM + r) * MM_LDS + c * 8, ok ? A + (size_t)src * lda + k : A, ok ? 16 : 0);
     }
-    for (int i = tid; i < MM_BROWS * 8; i += MM_THREADS) {
-      const int r = i >> 3, c = i & 7, k = k0 + c * 8;
+    for (int i = tid; i < MM_BROWS * CH; i += MM_THREADS) {
+      const int r = i / CH, c = i % CH, k = k0 + c * 8;
       const int n = FIRST ? n0 + (r & 63) : n0 + r;
       const bf16* base = (FIRST && r >= 64) ? w1 : w0;
       const bool ok = n < N && k < K;
@@ -126,7 +133,7 @@ __global__ void __launch_bounds__(MM_THREADS) moe_gemm_mma_kernel(
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         uint32_t a[4];
-        mm_ldmatrix_x4(a, as + (size_t)(mt * 16 + a_r) * MM_LDS + kk * 16 + a_k);
+        mm_ldmatrix_x4(a, as + (size_t)(row0 + mt * 16 + a_r) * MM_LDS + kk * 16 + a_k);
         mm_mma(acc[mt][0], a, b[0][0], b[0][1]);
         mm_mma(acc[mt][1], a, b[0][2], b[0][3]);
         mm_mma(acc[mt][2], a, b[1][0], b[1][1]);
@@ -141,7 +148,7 @@ __global__ void __launch_bounds__(MM_THREADS) moe_gemm_mma_kernel(
   for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int lr = mt * 16 + g + 8 * half;
+      const int lr = row0 + mt * 16 + g + 8 * half;
       if (arow[lr] < 0) continue;
       bf16* orow = out + ((size_t)tile * BM + lr) * N;
 #pragma unroll
@@ -167,13 +174,13 @@ __global__ void __launch_bounds__(MM_THREADS) moe_gemm_mma_kernel(
 template <int BM>
 static size_t mm_smem_bytes() { return (size_t)MM_STAGES * (BM + MM_BROWS) * MM_LDS * sizeof(bf16); }
 
-// tile: 16 or 64, the row tile that moe_align was called with.  first != 0: out [rows, N] = glu over x [T, K] gathered
+// tile: 16, 64 or 128, the row tile that moe_align was called with.  first != 0: out [rows, N] = glu over x [T, K] gathered
 // by sorted_slots, W0 / W1 [E, N, K]; first == 0: out [rows, N] = a [rows, K] times W0 [E, N, K].
 NHV_API int nhv_moe_gemm_mma(int tile, int first, void* out, const void* A, int lda, const void* W0, const void* W1,
                              const int* sorted_slots, const int* tile_expert, int max_tiles, int top, int N, int K,
                              float limit, float alpha, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
-  NHV_REQUIRE(tile == 16 || tile == 64, "moe_gemm (mma): the row tile is 16 or 64, not %d", tile);
+  NHV_REQUIRE(tile == 16 || tile == 64 || tile == 128, "moe_gemm (mma): the row tile is 16, 64 or 128, not %d", tile);
   NHV_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && top > 0, "moe_gemm (mma): bad sizes");
   NHV_REQUIRE(K % 8 == 0 && lda % 8 == 0 && N % 2 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W0 % 16) == 0 &&
                   (!first || ((uintptr_t)W1 % 16) == 0) && ((uintptr_t)out % 4) == 0,
@@ -188,11 +195,12 @@ NHV_API int nhv_moe_gemm_mma(int tile, int first, void* out, const void* A, int 
                                     (int)mm_smem_bytes<BM>()), "moe_gemm (mma)");                                     \
       attr = true;                                                                                                    \
     }                                                                                                                 \
-    nhv_launch(moe_gemm_mma_kernel<BM, F>, grid, MM_THREADS, mm_smem_bytes<BM>(), stream, (bf16*)out, (const bf16*)A, \
+    nhv_launch(moe_gemm_mma_kernel<BM, F>, grid, MmShape<BM>::THREADS, mm_smem_bytes<BM>(), stream, (bf16*)out, (const bf16*)A, \
                lda, (const bf16*)W0, (const bf16*)W1, sorted_slots, tile_expert, top, N, K, limit, alpha);            \
   } while (0)
   if (tile == 16) { if (first) GO(16, true); else GO(16, false); }
-  else { if (first) GO(64, true); else GO(64, false); }
+  else if (tile == 64) { if (first) GO(64, true); else GO(64, false); }
+  else { if (first) GO(128, true); else GO(128, false); }
 #undef GO
   NHV_CHECK_LAUNCH("moe_gemm (mma)");
   return 0;

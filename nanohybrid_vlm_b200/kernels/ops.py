@@ -371,13 +371,13 @@ def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: 
 
 
 MOE_ON_TENSOR_CORES = True      # tests switch it off to compare with the CUDA-core products at the same shapes
-MOE_TILE = 0                    # rows per tile of the tensor-core products: 0 chooses by the step; tests set 16 or 64
+MOE_TILE = 0                    # rows per tile of the tensor-core products: 0 chooses by the step; tests set 16, 64, 128
 
 
 def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
     """Every chosen expert's output for every token: orders the slots of ids [T, top] by expert and runs the experts' two
-    products over that order: bfloat16 with sizes in steps of 8 on the tensor cores (tiles of 64 rows where an expert
-    sees many rows, of 16 where it sees few and the products stream the weights), everything else on the CUDA cores.
+    products over that order: bfloat16 with sizes in steps of 8 on the tensor cores (tiles of 128 or 64 rows where an
+    expert sees many rows, of 16 where it sees few and the products stream the weights), everything else on the CUDA cores.
     Returns (y [rows, width], one row per slot that chose a real expert, and slot_pos [T * top] int32, the row of each
     slot or -1)."""
     E, ff, width = gate.shape
@@ -385,7 +385,7 @@ def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
     mma = MOE_ON_TENSOR_CORES and x.dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0
     tile = MOE_TILE_SIMT
     if mma:
-        tile = MOE_TILE or (64 if ids.numel() >= 24 * E else 16)
+        tile = MOE_TILE or (128 if ids.numel() >= 192 * E else 64 if ids.numel() >= 24 * E else 16)
     sorted_slots, slot_pos, tile_expert = moe_align(ids, E, tile)
     rows = sorted_slots.numel()
     act = torch.empty(rows, ff, dtype=x.dtype, device=x.device)

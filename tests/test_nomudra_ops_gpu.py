@@ -322,11 +322,12 @@ def plain_moe_sum(x, gate, up, down, ids, weights, limit, shared, sg):
     return out
 
 
-@pytest.mark.parametrize("path", ["float32", "bfloat16_cuda_cores", "bfloat16_tile16", "bfloat16_tile64", "bfloat16_auto"])
+@pytest.mark.parametrize("path", ["float32", "bfloat16_cuda_cores", "bfloat16_tile16", "bfloat16_tile64", "bfloat16_tile128",
+                                  "bfloat16_auto"])
 @pytest.mark.parametrize("T,E,I0,top,W,ff", [(1, 8, 2, 3, 64, 48), (5, 4, 0, 2, 128, 40), (300, 6, 2, 3, 96, 72),
                                             (70, 16, 1, 4, 200, 136), (9, 3, 1, 2, 100, 36)])
 def test_experts_and_their_sum(ops, path, T, E, I0, top, W, ff):
-    """Every path of the experts' products (CUDA cores in both types; tensor cores with tiles of 16 and of 64 rows) with
+    """Every path of the experts' products (CUDA cores in both types; tensor cores with tiles of 16, 64 and 128 rows) with
     identity choices, an expert that no token chooses, and the gated shared term.  The tokens' choices are drawn, not
     routed: each token gets `top` different outputs."""
     dtype = torch.float32 if path == "float32" else torch.bfloat16
@@ -347,7 +348,7 @@ def test_experts_and_their_sum(ops, path, T, E, I0, top, W, ff):
     sg = torch.full((T, 3), float("nan"))
     sg[:, 1] = torch.randn(T, generator=g)
     ops.MOE_ON_TENSOR_CORES = path != "bfloat16_cuda_cores"
-    ops.MOE_TILE = {"bfloat16_tile16": 16, "bfloat16_tile64": 64}.get(path, 0)
+    ops.MOE_TILE = {"bfloat16_tile16": 16, "bfloat16_tile64": 64, "bfloat16_tile128": 128}.get(path, 0)
     try:
         y, slot_pos = ops.moe_experts(dev(x), dev(gate), dev(up), dev(down), dev(ids), 1.5, 1.702)
     finally:
@@ -373,7 +374,7 @@ def test_experts_tensor_core_paths_equal_the_cuda_cores(ops):
     down = (torch.randn(E, W, ff, generator=g) * 0.1).bfloat16()
     ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).int()
     outs = []
-    for on, tile in ((False, 0), (True, 16), (True, 64)):
+    for on, tile in ((False, 0), (True, 16), (True, 64), (True, 128)):
         ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE = on, tile
         try:
             y, pos = ops.moe_experts(dev(x), dev(gate), dev(up), dev(down), dev(ids), 1.5, 1.702)
