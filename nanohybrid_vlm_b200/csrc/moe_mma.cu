@@ -65,10 +65,11 @@ __global__ void __launch_bounds__(MmShape<BM>::THREADS) moe_gemm_mma_kernel(
   bf16* Bs = As + MM_STAGES * BM * MM_LDS;                   // [STAGES][BROWS][LDS]
   __shared__ int arow[BM];
   pdl_prologue();
-  const int tile = blockIdx.x;
+  // panels of one tile of rows are neighbours in the grid: they run together and share the tile's rows in L2
+  const int tile = blockIdx.y;
   const int e = tile_expert[tile];
   if (e < 0) return;
-  const int n0 = blockIdx.y * (FIRST ? 64 : 128);
+  const int n0 = blockIdx.x * (FIRST ? 64 : 128);
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = (tid >> 5) & 3, row0 = (tid >> 7) * MmShape<BM>::WM;       // column quarter, first row of the warp
   if (tid < BM) {
@@ -185,8 +186,8 @@ NHV_API int nhv_moe_gemm_mma(int tile, int first, void* out, const void* A, int 
   NHV_REQUIRE(K % 8 == 0 && lda % 8 == 0 && N % 2 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W0 % 16) == 0 &&
                   (!first || ((uintptr_t)W1 % 16) == 0) && ((uintptr_t)out % 4) == 0,
               "moe_gemm (mma): rows of A and of the weights must start on 16-byte boundaries (K %d, lda %d)", K, lda);
-  dim3 grid(max_tiles, (N + (first ? 64 : 128) - 1) / (first ? 64 : 128));
-  NHV_REQUIRE(grid.y <= 65535, "moe_gemm (mma): %d output columns are beyond the grid's reach", N);
+  dim3 grid((N + (first ? 64 : 128) - 1) / (first ? 64 : 128), max_tiles);
+  NHV_REQUIRE(grid.y <= 65535, "moe_gemm (mma): %d tiles of rows are beyond the grid's reach", max_tiles);
 #define GO(BM, F)                                                                                                     \
   do {                                                                                                                \
     static bool attr = false;                                                                                         \

@@ -54,6 +54,8 @@ _SIGNATURES = {
     "nhv_moe_align": [P, I, I, I, P, P, P, P],
     "nhv_moe_gemm_simt": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
     "nhv_moe_gemm_mma": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
+    "nhv_moe_gather_rows": [P, P, P, I, I, I, P],
+    "nhv_moe_gemm_tcgen05": [I, P, P, P, P, I, P, P, I, I, I, F, F, P],
     "nhv_moe_combine": [I, P, P, P, P, P, I, P, P, P, I, I, I, I, P],
     "nhv_attention_simt_ex": [I, P, I, P, I, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P],
 }

@@ -371,13 +371,16 @@ def moe_experts_simt(act, y, x, gate, up, down, sorted_slots, tile_expert, top: 
 
 
 MOE_ON_TENSOR_CORES = True      # tests switch it off to compare with the CUDA-core products at the same shapes
-MOE_TILE = 0                    # rows per tile of the tensor-core products: 0 chooses by the step; tests set 16, 64, 128
+MOE_TILE = 0                    # rows per tile of the mma.sync products: 0 chooses by the step; tests set 16, 64, 128
+MOE_TCGEN05 = None              # the tcgen05 products: None where an expert sees many rows; tests set True (always) or False
+MOE_TCGEN05_TILE = 128          # rows per tile of the tcgen05 products (ROWS of csrc/moe_tcgen05.cu)
 
 
 def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
     """Every chosen expert's output for every token: orders the slots of ids [T, top] by expert and runs the experts' two
-    products over that order: bfloat16 with sizes in steps of 8 on the tensor cores (tiles of 128 or 64 rows where an
-    expert sees many rows, of 16 where it sees few and the products stream the weights), everything else on the CUDA cores.
+    products over that order: bfloat16 with sizes in steps of 8 on the tensor cores (tcgen05 with tiles of 128 rows
+    where an expert sees about a hundred rows or more; mma.sync with tiles of 64 rows below that and of 16 where it
+    sees few and the products stream the weights), everything else on the CUDA cores.
     Returns (y [rows, width], one row per slot that chose a real expert, and slot_pos [T * top] int32, the row of each
     slot or -1)."""
     E, ff, width = gate.shape
@@ -386,6 +389,8 @@ def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
     tile = MOE_TILE_SIMT
     if mma:
         tile = MOE_TILE or (128 if ids.numel() >= 192 * E else 64 if ids.numel() >= 24 * E else 16)
+    if mma and (MOE_TCGEN05 or (MOE_TCGEN05 is None and not MOE_TILE and ids.numel() >= 96 * E)):
+        return _moe_experts_tcgen05(x, gate, up, down, ids, limit, alpha)
     sorted_slots, slot_pos, tile_expert = moe_align(ids, E, tile)
     rows = sorted_slots.numel()
     act = torch.empty(rows, ff, dtype=x.dtype, device=x.device)
@@ -403,6 +408,29 @@ def moe_experts(x, gate, up, down, ids, limit: float, alpha: float):
          sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, ff, width, float(limit), float(alpha), stream_ptr())
     call("nhv_moe_gemm_mma", tile, 0, y.data_ptr(), act.data_ptr(), ff, down.data_ptr(), None,
          sorted_slots.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff, 0.0, 0.0, stream_ptr())
+    return y, slot_pos
+
+
+def _moe_experts_tcgen05(x, gate, up, down, ids, limit: float, alpha: float):
+    """``moe_experts`` for prompts in bfloat16: tiles of 128 rows per expert, the tokens' rows gathered into that order
+    (so that a tile is one TMA box), both products with tcgen05.mma and tensor-memory accumulators."""
+    _need_cuda(x, gate, up, down, ids)
+    for name, t in (("x", x), ("gate", gate), ("up", up), ("down", down)):
+        _contig(name, t)
+    E, ff, width = gate.shape
+    top = ids.shape[1]
+    assert up.shape == gate.shape and down.shape == (E, width, ff) and x.shape[1] == width
+    assert x.dtype == gate.dtype == up.dtype == down.dtype == torch.bfloat16
+    sorted_slots, slot_pos, tile_expert = moe_align(ids, E, MOE_TCGEN05_TILE)
+    rows, tiles = sorted_slots.numel(), tile_expert.numel()
+    xs = torch.empty(rows, width, dtype=x.dtype, device=x.device)
+    act = torch.empty(rows, ff, dtype=x.dtype, device=x.device)
+    y = torch.empty(rows, width, dtype=x.dtype, device=x.device)
+    call("nhv_moe_gather_rows", xs.data_ptr(), x.data_ptr(), sorted_slots.data_ptr(), rows, top, width, stream_ptr())
+    call("nhv_moe_gemm_tcgen05", 1, act.data_ptr(), xs.data_ptr(), gate.data_ptr(), up.data_ptr(), E, sorted_slots.data_ptr(),
+         tile_expert.data_ptr(), tiles, ff, width, float(limit), float(alpha), stream_ptr())
+    call("nhv_moe_gemm_tcgen05", 0, y.data_ptr(), act.data_ptr(), down.data_ptr(), None, E, sorted_slots.data_ptr(),
+         tile_expert.data_ptr(), tiles, width, ff, 0.0, 0.0, stream_ptr())
     return y, slot_pos
 
 
@@ -1029,7 +1057,7 @@ def _register_library_sources() -> None:
     import ctypes
     from .library import load_library
     lib = load_library()
-    for name in ("gemm_slab", "gemm_stream_k", "gemm_tcgen05"):
+    for name in ("gemm_slab", "gemm_stream_k", "gemm_tcgen05", "moe_tcgen05"):
         word = getattr(lib, f"nhv_{name}_error_word")
         word.restype, word.argtypes = ctypes.c_void_p, []
         take = getattr(lib, f"nhv_{name}_error")

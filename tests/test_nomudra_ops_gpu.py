@@ -323,15 +323,15 @@ def plain_moe_sum(x, gate, up, down, ids, weights, limit, shared, sg):
 
 
 @pytest.mark.parametrize("path", ["float32", "bfloat16_cuda_cores", "bfloat16_tile16", "bfloat16_tile64", "bfloat16_tile128",
-                                  "bfloat16_auto"])
+                                  "bfloat16_tcgen05", "bfloat16_auto"])
 @pytest.mark.parametrize("T,E,I0,top,W,ff", [(1, 8, 2, 3, 64, 48), (5, 4, 0, 2, 128, 40), (300, 6, 2, 3, 96, 72),
                                             (70, 16, 1, 4, 200, 136), (9, 3, 1, 2, 100, 36)])
 def test_experts_and_their_sum(ops, path, T, E, I0, top, W, ff):
-    """Every path of the experts' products (CUDA cores in both types; tensor cores with tiles of 16, 64 and 128 rows) with
+    """Every path of the experts' products (CUDA cores in both types; mma.sync with tiles of 16, 64 and 128 rows; tcgen05) with
     identity choices, an expert that no token chooses, and the gated shared term.  The tokens' choices are drawn, not
     routed: each token gets `top` different outputs."""
     dtype = torch.float32 if path == "float32" else torch.bfloat16
-    if path.startswith("bfloat16_tile") and (W % 8 or ff % 8):
+    if path.startswith(("bfloat16_tile", "bfloat16_tcgen05")) and (W % 8 or ff % 8):
         pytest.skip("the tensor-core products take sizes in steps of 8")
     g = torch.Generator().manual_seed(T * 7 + E)
     x = torch.randn(T, W, generator=g).to(dtype)
@@ -349,10 +349,12 @@ def test_experts_and_their_sum(ops, path, T, E, I0, top, W, ff):
     sg[:, 1] = torch.randn(T, generator=g)
     ops.MOE_ON_TENSOR_CORES = path != "bfloat16_cuda_cores"
     ops.MOE_TILE = {"bfloat16_tile16": 16, "bfloat16_tile64": 64, "bfloat16_tile128": 128}.get(path, 0)
+    ops.MOE_TCGEN05 = True if path == "bfloat16_tcgen05" else None
     try:
         y, slot_pos = ops.moe_experts(dev(x), dev(gate), dev(up), dev(down), dev(ids), 1.5, 1.702)
+        ops.raise_wait_errors()
     finally:
-        ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE = True, 0
+        ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE, ops.MOE_TCGEN05 = True, 0, None
     out = torch.full((T, W), float("nan"), dtype=dtype, device="cuda")
     ops.moe_combine(out, y, dev(x), dev(ids), dev(weights), slot_pos, E, dev(shared), dev(sg)[:, 1])
     want = plain_moe_sum(x.to(F64), gate.to(F64), up.to(F64), down.to(F64), ids, weights.to(F64), 1.5, shared.to(F64),
@@ -365,8 +367,8 @@ def test_experts_and_their_sum(ops, path, T, E, I0, top, W, ff):
 
 
 def test_experts_tensor_core_paths_equal_the_cuda_cores(ops):
-    """In bfloat16 the tensor-core products round where the CUDA-core products round, so both tiles give nearly the
-    same numbers as the CUDA cores (sums in another order), far closer than bfloat16 is to float64."""
+    """In bfloat16 the tensor-core products round where the CUDA-core products round, so every tile and the tcgen05
+    products give nearly the same numbers as the CUDA cores (sums in another order), far closer than bfloat16 is to float64."""
     g = torch.Generator().manual_seed(1)
     T, E, top, W, ff = 150, 5, 2, 128, 96
     x = torch.randn(T, W, generator=g).bfloat16()
@@ -374,12 +376,12 @@ def test_experts_tensor_core_paths_equal_the_cuda_cores(ops):
     down = (torch.randn(E, W, ff, generator=g) * 0.1).bfloat16()
     ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).int()
     outs = []
-    for on, tile in ((False, 0), (True, 16), (True, 64), (True, 128)):
-        ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE = on, tile
+    for on, tile, tc in ((False, 0, False), (True, 16, False), (True, 64, False), (True, 128, False), (True, 0, True)):
+        ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE, ops.MOE_TCGEN05 = on, tile, tc
         try:
             y, pos = ops.moe_experts(dev(x), dev(gate), dev(up), dev(down), dev(ids), 1.5, 1.702)
         finally:
-            ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE = True, 0
+            ops.MOE_ON_TENSOR_CORES, ops.MOE_TILE, ops.MOE_TCGEN05 = True, 0, None
         outs.append(y[pos.long()].float().cpu())
     for other in outs[1:]:
         torch.testing.assert_close(other, outs[0], rtol=1e-2, atol=2e-3)
