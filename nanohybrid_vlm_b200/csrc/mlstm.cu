@@ -9,9 +9,9 @@
 //   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6),     q_t already times d^-1/2
 //
 // The columns of S are independent of one another (column j: S_j <- a S_j + b v_j k, o_j = S_j . q / den), so a
-// block takes (request, head, ML_COLS columns) and a column lives in the registers of ML_PARTS lanes, each with
-// d / ML_PARTS rows; every column block carries the rows of n as well (its own copy, so that no block reads what
-// another writes).  The gates of ML_CHUNK tokens are prepared together: their tanh and logsigmoid in parallel, the
+// block takes (request, head, ML_COLS columns) and a column lives in the registers of 8 or 16 lanes, each with
+// d / 8 or d / 16 rows; every column block carries the rows of n as well (its own copy, so that no block reads what
+// another writes).  The gates of a stage of tokens (64, or 32 for the largest heads) are prepared together: their tanh and logsigmoid in parallel, the
 // chain of maxima by one thread, the exponentials in parallel again.
 //
 // State of a slot: S transposed, [head][dv][d], then per (head, column block) the d rows of n and m.
@@ -21,8 +21,6 @@
 #include "nhv_common.cuh"
 
 constexpr int ML_COLS = 16;
-constexpr int ML_PARTS = 8;
-constexpr int ML_CHUNK = 32;
 
 __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -42,18 +40,20 @@ __device__ __forceinline__ void ml_load8(float (&o)[8], const __nv_bfloat16* p) 
   }
 }
 
-// Which row of its column a lane's r-th register holds.  VEC (d in steps of 32): groups of four consecutive rows, so
-// that one 16-byte read of k and one of q from shared memory serve four rows; else rows ML_PARTS apart.
-template <bool VEC> __device__ __forceinline__ int ml_row(int part, int r) {
-  return VEC ? ((r >> 2) * (4 * ML_PARTS) + part * 4 + (r & 3)) : (part + r * ML_PARTS);
+// Which row of its column a lane's r-th register holds (a column lives in PARTS lanes).  VEC (d in steps of 4 * PARTS):
+// groups of four consecutive rows, so that one 16-byte read of k and one of q from shared memory serve four rows, and
+// two neighbouring rows share a packed fp32x2 instruction; else rows PARTS apart.
+template <bool VEC, int PARTS> __device__ __forceinline__ int ml_row(int part, int r) {
+  return VEC ? ((r >> 2) * (4 * PARTS) + part * 4 + (r & 3)) : (part + r * PARTS);
 }
 
 // VEC also reads the tokens' rows of proj eight elements at a time (the host checks sizes and alignment).
-template <typename T, int R, bool VEC>
+template <typename T, int R, bool VEC, int ML_PARTS>
 __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
     float* __restrict__ y, const T* __restrict__ proj, int proj_stride, const float* __restrict__ gates, int gate_stride,
     const float* __restrict__ gate_bias, float cap, float* __restrict__ state, long state_stride,
     const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ slots, int H, int d, int dv) {
+  constexpr int stage_tokens = (R * ML_PARTS > 256) ? 32 : 64;   // tokens per stage: what fits a block's shared memory
   extern __shared__ __align__(16) float smem[];
   pdl_prologue();
   const int s = blockIdx.x, h = blockIdx.y, cb = blockIdx.z, col0 = cb * ML_COLS;
@@ -67,11 +67,11 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
     return;
   }
   float* ks = smem;                          // [CHUNK][d]
-  float* qs = ks + ML_CHUNK * d;             // [CHUNK][d], times d^-1/2
-  float* vs = qs + ML_CHUNK * d;             // [CHUNK][COLS]
-  float* ga = vs + ML_CHUNK * ML_COLS;       // [CHUNK] decay of the old state; before that the log forget gate
-  float* gb = ga + ML_CHUNK;                 // [CHUNK] weight of the new pair; before that the log input gate
-  float* gm = gb + ML_CHUNK;                 // [CHUNK + 1] m before each token and after the last; then exp(-m_t)
+  float* qs = ks + stage_tokens * d;             // [CHUNK][d], times d^-1/2
+  float* vs = qs + stage_tokens * d;             // [CHUNK][COLS]
+  float* ga = vs + stage_tokens * ML_COLS;       // [CHUNK] decay of the old state; before that the log forget gate
+  float* gb = ga + stage_tokens;                 // [CHUNK] weight of the new pair; before that the log input gate
+  float* gm = gb + stage_tokens;                 // [CHUNK + 1] m before each token and after the last; then exp(-m_t)
   const int cl = tid / ML_PARTS, part = tid % ML_PARTS;
   const bool live = cl < ncol;
   const int col = col0 + (live ? cl : 0);
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
   float S[R], Nn[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = ml_row<VEC>(part, r);
+    const int i = ml_row<VEC, ML_PARTS>(part, r);
     S[r] = (live && !fresh && i < d) ? st[i] : 0.f;
     Nn[r] = (!fresh && i < d) ? nm[i] : 0.f;
   }
@@ -90,8 +90,8 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
   const float qscale = 1.0f / sqrtf((float)d);
   const float bi = gate_bias[h], bf = gate_bias[H + h];
   const int q_off = h * d, k_off = H * d + h * d, v_off = 2 * H * d + h * dv + col0;
-  for (int c0 = 0; c0 < n; c0 += ML_CHUNK) {
-    const int cn = min(ML_CHUNK, n - c0);
+  for (int c0 = 0; c0 < n; c0 += stage_tokens) {
+    const int cn = min(stage_tokens, n - c0);
     __syncthreads();
     if (VEC) {
       const int d8 = d >> 3;
@@ -160,21 +160,31 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
       const float* qt = qs + tt * d;
       float acc[4] = {0.f, 0.f, 0.f, 0.f}, accn[4] = {0.f, 0.f, 0.f, 0.f};
       if (VEC) {
+        // two neighbouring rows per packed instruction (each half rounded as the scalar operation would be)
+        const f32x2 a2 = f2_pack(a, a), bv2 = f2_pack(bv, bv), b2 = f2_pack(b, b);
+        f32x2 so2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)}, sn2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
 #pragma unroll
         for (int j = 0; j < R / 4; ++j) {
           const int i0 = j * (4 * ML_PARTS) + part * 4;
           if (i0 < d) {
             const float4 k4 = *reinterpret_cast<const float4*>(kt + i0), q4 = *reinterpret_cast<const float4*>(qt + i0);
-            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+            const f32x2 kk[2] = {f2_pack(k4.x, k4.y), f2_pack(k4.z, k4.w)}, qq[2] = {f2_pack(q4.x, q4.y), f2_pack(q4.z, q4.w)};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              S[4 * j + e] = fmaf(a, S[4 * j + e], bv * kk[e]);
-              Nn[4 * j + e] = fmaf(a, Nn[4 * j + e], b * kk[e]);
-              acc[e] = fmaf(S[4 * j + e], qq[e], acc[e]);
-              accn[e] = fmaf(Nn[4 * j + e], qq[e], accn[e]);
+            for (int e = 0; e < 2; ++e) {
+              f32x2 s2 = f2_pack(S[4 * j + 2 * e], S[4 * j + 2 * e + 1]), n2 = f2_pack(Nn[4 * j + 2 * e], Nn[4 * j + 2 * e + 1]);
+              s2 = f2_fma(a2, s2, f2_mul(bv2, kk[e]));
+              n2 = f2_fma(a2, n2, f2_mul(b2, kk[e]));
+              so2[e] = f2_fma(s2, qq[e], so2[e]);
+              sn2[e] = f2_fma(n2, qq[e], sn2[e]);
+              f2_unpack(s2, S[4 * j + 2 * e], S[4 * j + 2 * e + 1]);
+              f2_unpack(n2, Nn[4 * j + 2 * e], Nn[4 * j + 2 * e + 1]);
             }
           }
         }
+        f2_unpack(so2[0], acc[0], acc[1]);
+        f2_unpack(so2[1], acc[2], acc[3]);
+        f2_unpack(sn2[0], accn[0], accn[1]);
+        f2_unpack(sn2[1], accn[2], accn[3]);
       } else {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -200,7 +210,7 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = ml_row<VEC>(part, r);
+    const int i = ml_row<VEC, ML_PARTS>(part, r);
     if (i < d) {
       if (live) st[i] = S[r];
       if (cl == 0) nm[i] = Nn[r];
@@ -219,39 +229,55 @@ NHV_API int nhv_mlstm_state_floats(int H, int d, int dv) {
 // before bias and cap), gate_bias [2*H] fp32, y [T, H*dv] fp32.
 NHV_API int nhv_mlstm_scan(int dtype, float* y, const void* proj, int proj_stride, const float* gates, int gate_stride,
                            const float* gate_bias, float cap, float* state, long state_stride, const int* cu_q,
-                           const int* q_start, const int* slots, int n_seqs, int n_tokens, int H, int d, int dv,
+                           const int* q_start, const int* slots, int n_seqs, int n_tokens, int H, int d, int dv, int lanes,
                            cudaStream_t stream) {
   if (n_tokens == 0 || n_seqs == 0) return 0;
   NHV_REQUIRE(H > 0 && d > 0 && dv > 0 && cap > 0.f, "mlstm_scan: bad sizes");
-  NHV_REQUIRE(d <= 64 * ML_PARTS, "mlstm_scan: a key head of %d elements is beyond the supported %d", d, 64 * ML_PARTS);
+  NHV_REQUIRE(d <= 512, "mlstm_scan: a key head of %d elements is beyond the supported 512", d);
   NHV_REQUIRE(state_stride >= (long)nhv_mlstm_state_floats(H, d, dv), "mlstm_scan: the state holds fewer floats than S, n and m need");
-  const int rows = (d + ML_PARTS - 1) / ML_PARTS;
-  const size_t smem = ((size_t)ML_CHUNK * (2 * d + ML_COLS) + 3 * ML_CHUNK + 1) * sizeof(float);
+  // lanes per column of the memory: 8, or 16 (twice the warps for the same columns, half the rows in each lane) where
+  // heads are large enough to fill them; `lanes` 8 or 16 asks for one of them
+  const int parts = (lanes == 8 || lanes == 16) ? lanes : (d >= 64 ? 16 : 8);
+  const int rows = (d + parts - 1) / parts;
+  const int r_lanes = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : rows <= 32 ? 32 : 64;      // the kernel's R
+  const int chunk = r_lanes * parts > 256 ? 32 : 64;           // the kernel's tokens per stage
+  const size_t smem = ((size_t)chunk * (2 * d + ML_COLS) + 3 * chunk + 1) * sizeof(float);
   dim3 grid(n_seqs, H, (dv + ML_COLS - 1) / ML_COLS);
   // rows in groups of four and tokens read eight elements at a time, where sizes and alignment allow it
   const size_t item = dtype == NHV_F32 ? 4 : 2;
-  const bool vec = d % (4 * ML_PARTS) == 0 && dv % 8 == 0 && proj_stride % 8 == 0 && ((uintptr_t)proj % 16) == 0 &&
+  const bool vec = d % (4 * parts) == 0 && dv % 8 == 0 && proj_stride % 8 == 0 && ((uintptr_t)proj % 16) == 0 &&
                    ((size_t)H * d * item) % 16 == 0;
-#define SCAN(T, R, V)                                                                                               \
+#define SCAN(T, R, V, P)                                                                                            \
   do {                                                                                                              \
     if (smem > 48 * 1024)                                                                                           \
-      NHV_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, R, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+      NHV_CUDA(cudaFuncSetAttribute(mlstm_scan_kernel<T, R, V, P>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                     (int)smem), "mlstm_scan");                                                      \
-    nhv_launch(mlstm_scan_kernel<T, R, V>, grid, ML_COLS * ML_PARTS, smem, stream, y, (const T*)proj, proj_stride,  \
+    nhv_launch(mlstm_scan_kernel<T, R, V, P>, grid, ML_COLS * P, smem, stream, y, (const T*)proj, proj_stride,      \
                gates, gate_stride, gate_bias, cap, state, state_stride, cu_q, q_start, slots, H, d, dv);            \
   } while (0)
-#define LAUNCH(T)                                                   \
-  do {                                                              \
-    if (rows <= 4) { if (vec) SCAN(T, 4, true); else SCAN(T, 4, false); }            \
-    else if (rows <= 8) { if (vec) SCAN(T, 8, true); else SCAN(T, 8, false); }       \
-    else if (rows <= 16) { if (vec) SCAN(T, 16, true); else SCAN(T, 16, false); }    \
-    else if (rows <= 32) { if (vec) SCAN(T, 32, true); else SCAN(T, 32, false); }    \
-    else { if (vec) SCAN(T, 64, true); else SCAN(T, 64, false); }                    \
+#define SCAN_V(T, R, P)                                     \
+  do {                                                      \
+    if (vec) SCAN(T, R, true, P); else SCAN(T, R, false, P); \
+  } while (0)
+#define SCAN_R(T, P)                         \
+  do {                                       \
+    if (rows <= 4) SCAN_V(T, 4, P);          \
+    else if (rows <= 8) SCAN_V(T, 8, P);     \
+    else if (rows <= 16) SCAN_V(T, 16, P);   \
+    else if (rows <= 32) SCAN_V(T, 32, P);   \
+    else SCAN_V(T, 64, P);                   \
+  } while (0)
+#define LAUNCH(T)                            \
+  do {                                       \
+    if (parts == 16) SCAN_R(T, 16);          \
+    else SCAN_R(T, 8);                       \
   } while (0)
   if (dtype == NHV_F32) LAUNCH(float);
   else if (dtype == NHV_BF16) LAUNCH(__nv_bfloat16);
   else NHV_REQUIRE(false, "mlstm_scan: unknown dtype %d", dtype);
 #undef LAUNCH
+#undef SCAN_R
+#undef SCAN_V
 #undef SCAN
   NHV_CHECK_LAUNCH("mlstm_scan");
   return 0;

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "nhv_sigmoid_mul": [I, P, I, P, I, P, I, I, I, P],
     "nhv_add_row_bias": [I, P, P, I, I, P],
     "nhv_clamped_glu": [I, P, P, I, I, F, F, P],
-    "nhv_mlstm_scan": [I, P, P, I, P, I, P, F, P, ctypes.c_long, P, P, P, I, I, I, I, I, P],
+    "nhv_mlstm_scan": [I, P, P, I, P, I, P, F, P, ctypes.c_long, P, P, P, I, I, I, I, I, I, P],
     "nhv_moe_route": [P, P, P, I, P, I, I, I, I, I, P],
     "nhv_moe_align": [P, I, I, I, P, P, P, P],
     "nhv_moe_gemm_simt": [I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P],

@@ -289,6 +289,7 @@ def clamped_glu(out, gate_up, limit: float, alpha: float) -> None:
 
 
 MLSTM_COLUMN_BLOCK = 16     # columns of the memory that one block of the scan carries (ML_COLS of csrc/mlstm.cu)
+MLSTM_LANES = 0             # lanes per column of the memory: 0 is the kernel's choice; tests set 8 or 16
 
 
 def mlstm_state_floats(H: int, d: int, dv: int) -> int:
@@ -310,7 +311,7 @@ def mlstm_scan(y, proj, gates, gate_bias, cap: float, state, batch, H: int, d: i
     assert state.shape[1] >= mlstm_state_floats(H, d, dv)
     call("nhv_mlstm_scan", dtype_code(proj), y.data_ptr(), proj.data_ptr(), proj.stride(0), gates.data_ptr(), gates.stride(0),
          gate_bias.data_ptr(), float(cap), state.data_ptr(), state.stride(0), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
-         batch.state_slots.data_ptr(), batch.n_seqs, T, H, d, dv, stream_ptr())
+         batch.state_slots.data_ptr(), batch.n_seqs, T, H, d, dv, MLSTM_LANES, stream_ptr())
 
 
 def moe_route(ids, weights, logits, correction, n_outputs: int, n_groups: int, keep: int) -> None:

@@ -248,10 +248,19 @@ def plain_scan(proj, gates, bias, cap, H, d, dv):
     return pn.mlstm_recurrence(q, k, v, i, f).reshape(T, H * dv)
 
 
+@pytest.fixture(params=[0, 8, 16], ids=lambda p: f"lanes{p}")
+def lanes(request, ops):
+    """Both forms of the scan: a column of the memory in 8 or in 16 lanes (0: the kernel's choice)."""
+    ops.MLSTM_LANES = request.param
+    yield request.param
+    ops.MLSTM_LANES = 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,d,dv,cap,spread", [(2, 24, 40, 15.0, 6.0), (1, 100, 16, 4.0, 8.0), (3, 16, 130, 10.0, 1.0),
-                                               (1, 256, 8, 15.0, 3.0), (2, 7, 5, 2.0, 3.0), (2, 128, 128, 15.0, 4.0)])
-def test_mlstm_scan_over_portions_and_reused_slots(ops, dtype, H, d, dv, cap, spread):
+                                               (1, 256, 8, 15.0, 3.0), (2, 7, 5, 2.0, 3.0), (2, 128, 128, 15.0, 4.0),
+                                               (1, 64, 24, 15.0, 4.0), (1, 512, 16, 15.0, 2.0)])
+def test_mlstm_scan_over_portions_and_reused_slots(ops, lanes, dtype, H, d, dv, cap, spread):
     """Three requests cut into portions of 1, 2 and more tokens, their states in slots 1, 3, 0 of a poisoned pool; gates
     spread so wide that the cap and the running maximum matter (input gates far above and below the forget gates);
     then a new request in a used slot, which must start from zeros and a maximum of 0."""
