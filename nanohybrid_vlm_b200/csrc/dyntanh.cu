@@ -8,7 +8,8 @@
 //                      s = stream[src] + (a ? f_post(a[src]) : 0)     (32-bit; written back unless rows are gathered;
 //                                                                      without f_post the addend is added as it is)
 //                      out[r] = f_pre(s)                              (rounded once to the storage type)
-//                    with src = rows[r] or r.  One kernel does the add of the last sub-block and the norm of the next.
+//                    with src = rows[r] or r.  One kernel does the add of the last sub-block and the norm of the next;
+//                    elementwise over rows x width, so a decode step of a few rows spreads over many blocks.
 //
 // All arithmetic is fp32 (tanhf); alpha, w and b are stored in the model's type.
 #include <math.h>
@@ -89,26 +90,70 @@ NHV_API int nhv_embed_dyntanh(int dtype, float* out, const void* table, const in
   return 0;
 }
 
-// One block per output row.
-template <typename T>
-__global__ void dyntanh_stream_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ a,
-                                      DytParams<T> post, DytParams<T> pre, const int* __restrict__ rows, int width,
-                                      int write_stream) {
+// Four neighbouring columns of a row per thread (width in steps of 4), or one; the elements do not depend on one
+// another, so a step of few rows still fills the device.
+template <typename T> __device__ __forceinline__ void dyt_load4(float (&o)[4], const T* p);
+template <> __device__ __forceinline__ void dyt_load4<float>(float (&o)[4], const float* p) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+template <> __device__ __forceinline__ void dyt_load4<__nv_bfloat16>(float (&o)[4], const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+__device__ __forceinline__ void dyt_store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void dyt_store4(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+  h[0] = __floats2bfloat162_rn(v[0], v[1]);
+  h[1] = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) dyntanh_stream_kernel(T* __restrict__ out, float* __restrict__ stream,
+                                                             const T* __restrict__ a, DytParams<T> post, DytParams<T> pre,
+                                                             const int* __restrict__ rows, int width, int write_stream,
+                                                             size_t total) {
   pdl_prologue();
-  const int r = blockIdx.x;
-  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
-  float* srow = stream + src * width;
-  const T* arow = a ? a + src * width : nullptr;
   const float a_pre = to_f32<T>(pre.alpha[0]);
-  const bool has_post = arow && post.alpha;                     // an addend without a norm of its own is added as it is
+  const bool has_post = a && post.alpha;                        // an addend without a norm of its own is added as it is
   const float a_post = has_post ? to_f32<T>(post.alpha[0]) : 0.f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float s = srow[c];
-    if (arow) {
-      s += has_post ? dyt_apply<T>(to_f32<T>(arow[c]), a_post, post, c) : to_f32<T>(arow[c]);
-      if (write_stream) srow[c] = s;
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < total; i += (size_t)gridDim.x * blockDim.x * VEC) {
+    const size_t r = i / width;
+    const int c = (int)(i - r * width);
+    const size_t src = (rows ? (size_t)rows[r] : r) * width + c;
+    float s[VEC], y[VEC];
+    if constexpr (VEC == 4) {
+      float s4[4];
+      dyt_load4<float>(s4, stream + src);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) s[e] = s4[e];
+      if (a) {
+        float a4[4];
+        dyt_load4<T>(a4, a + src);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s[e] += has_post ? dyt_apply<T>(a4[e], a_post, post, c + e) : a4[e];
+        if (write_stream) {
+          dyt_store4(stream + src, s);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) y[e] = dyt_apply<T>(s[e], a_pre, pre, c + e);
+      dyt_store4(out + i, y);
+    } else {
+      s[0] = stream[src];
+      if (a) {
+        const float av = to_f32<T>(a[src]);
+        s[0] += has_post ? dyt_apply<T>(av, a_post, post, c) : av;
+        if (write_stream) stream[src] = s[0];
+      }
+      out[i] = from_f32<T>(dyt_apply<T>(s[0], a_pre, pre, c));
     }
-    out[(size_t)r * width + c] = from_f32<T>(dyt_apply<T>(s, a_pre, pre, c));
   }
 }
 
@@ -119,14 +164,17 @@ NHV_API int nhv_dyntanh_stream(int dtype, void* out, float* stream, const void* 
   if (n_rows == 0) return 0;
   NHV_REQUIRE(n_rows > 0 && width > 0, "dyntanh_stream: bad sizes");
   NHV_REQUIRE(!post_alpha || (post_w && post_b), "dyntanh_stream: a norm is alpha, weight and bias together");
-  const int threads = width >= 1024 ? 256 : 128;
-#define GO(T)                                                                                                     \
-  nhv_launch(dyntanh_stream_kernel<T>, n_rows, threads, 0, stream_, (T*)out, stream, (const T*)a,                 \
+  const size_t total = (size_t)n_rows * width;
+  const bool vec = width % 4 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)stream % 16) == 0 && ((uintptr_t)a % 16) == 0;
+  const size_t per_block = 256 * (vec ? 4 : 1);
+  const int blocks = (int)((total + per_block - 1) / per_block < 65535 * 8 ? (total + per_block - 1) / per_block : 65535 * 8);
+#define GO(T, V)                                                                                                  \
+  nhv_launch(dyntanh_stream_kernel<T, V>, blocks, 256, 0, stream_, (T*)out, stream, (const T*)a,                  \
              DytParams<T>{(const T*)post_alpha, (const T*)post_w, (const T*)post_b},                              \
              DytParams<T>{(const T*)pre_alpha, (const T*)pre_w, (const T*)pre_b}, rows, width,                    \
-             (write_stream && !rows) ? 1 : 0)
-  if (dtype == NHV_F32) GO(float);
-  else if (dtype == NHV_BF16) GO(__nv_bfloat16);
+             (write_stream && !rows) ? 1 : 0, total)
+  if (dtype == NHV_F32) { if (vec) GO(float, 4); else GO(float, 1); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, 4); else GO(__nv_bfloat16, 1); }
   else NHV_REQUIRE(false, "dyntanh_stream: unknown dtype %d", dtype);
 #undef GO
   NHV_CHECK_LAUNCH("dyntanh_stream");
