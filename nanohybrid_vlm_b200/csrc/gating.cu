@@ -4,19 +4,39 @@
 //   add_row_bias    x[t, c] += bias[c], in place                     (the bias of a projection whose product has none)
 //   clamped_glu     out[t, c] = g' * sigmoid(alpha * g') * (u' + 1), g' = min(gate, limit), u' = clamp(up, -limit, limit)
 //                   for gate_up [T, 2 I] with the gate in the first half of each row
+//
+// Each takes eight columns per thread where the width and the row strides are multiples of 8 and the pointers lie
+// on 16-byte boundaries, else one.
 #include <math.h>
 
 #include "nhv_common.cuh"
+#include "nhv_vec8.cuh"
 
-template <typename T>
-__global__ void sigmoid_mul_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ x, int x_stride,
+static inline int gating_blocks(size_t items) {
+  const size_t b = (items + 255) / 256;
+  return (int)(b < (size_t)1 << 20 ? b : (size_t)1 << 20);
+}
+static inline bool aligned16(const void* p) { return ((uintptr_t)p % 16) == 0; }
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+template <typename T, int VEC>
+__global__ void sigmoid_mul_kernel(T* out, int out_stride, const T* x, int x_stride,      // out may be x itself
                                    const T* __restrict__ g, int g_stride, int width, size_t total) {
   pdl_prologue();
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < total; i += (size_t)gridDim.x * blockDim.x * VEC) {
     const size_t t = i / width;
     const int c = (int)(i - t * width);
-    const float gv = to_f32<T>(g[t * g_stride + c]);
-    out[t * out_stride + c] = from_f32<T>(to_f32<T>(x[t * x_stride + c]) / (1.0f + expf(-gv)));
+    if constexpr (VEC == 8) {
+      float xv[8], gv[8];
+      nhv_load8(xv, x + t * x_stride + c);
+      nhv_load8(gv, g + t * g_stride + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xv[e] *= sigmoid_f(gv[e]);
+      nhv_store8(out + t * out_stride + c, xv);
+    } else {
+      out[t * out_stride + c] = from_f32<T>(to_f32<T>(x[t * x_stride + c]) * sigmoid_f(to_f32<T>(g[t * g_stride + c])));
+    }
   }
 }
 
@@ -25,33 +45,47 @@ NHV_API int nhv_sigmoid_mul(int dtype, void* out, int out_stride, const void* x,
   if (n_rows == 0) return 0;
   NHV_REQUIRE(n_rows > 0 && width > 0, "sigmoid_mul: bad sizes");
   const size_t total = (size_t)n_rows * width;
-  const int blocks = (int)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
-#define GO(T) \
-  nhv_launch(sigmoid_mul_kernel<T>, blocks, 256, 0, stream, (T*)out, out_stride, (const T*)x, x_stride, (const T*)g, g_stride, width, total)
-  if (dtype == NHV_F32) GO(float);
-  else if (dtype == NHV_BF16) GO(__nv_bfloat16);
+  const bool vec = width % 8 == 0 && out_stride % 8 == 0 && x_stride % 8 == 0 && g_stride % 8 == 0 && aligned16(out) &&
+                   aligned16(x) && aligned16(g);
+#define GO(T, V)                                                                                                     \
+  nhv_launch(sigmoid_mul_kernel<T, V>, gating_blocks(total / V), 256, 0, stream, (T*)out, out_stride, (const T*)x, x_stride, \
+             (const T*)g, g_stride, width, total)
+  if (dtype == NHV_F32) { if (vec) GO(float, 8); else GO(float, 1); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
   else NHV_REQUIRE(false, "sigmoid_mul: unknown dtype %d", dtype);
 #undef GO
   NHV_CHECK_LAUNCH("sigmoid_mul");
   return 0;
 }
 
-template <typename T>
+template <typename T, int VEC>
 __global__ void add_row_bias_kernel(T* __restrict__ x, const T* __restrict__ bias, int width, size_t total) {
   pdl_prologue();
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
-    x[i] = from_f32<T>(to_f32<T>(x[i]) + to_f32<T>(bias[i % width]));
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < total; i += (size_t)gridDim.x * blockDim.x * VEC) {
+    const int c = (int)(i % width);
+    if constexpr (VEC == 8) {
+      float xv[8], bv[8];
+      nhv_load8(xv, x + i);
+      nhv_load8(bv, bias + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xv[e] += bv[e];
+      nhv_store8(x + i, xv);
+    } else {
+      x[i] = from_f32<T>(to_f32<T>(x[i]) + to_f32<T>(bias[c]));
+    }
+  }
 }
 
 NHV_API int nhv_add_row_bias(int dtype, void* x, const void* bias, int n_rows, int width, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NHV_REQUIRE(n_rows > 0 && width > 0, "add_row_bias: bad sizes");
   const size_t total = (size_t)n_rows * width;
-  const int blocks = (int)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
-  if (dtype == NHV_F32) nhv_launch(add_row_bias_kernel<float>, blocks, 256, 0, stream, (float*)x, (const float*)bias, width, total);
-  else if (dtype == NHV_BF16)
-    nhv_launch(add_row_bias_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)bias, width, total);
+  const bool vec = width % 8 == 0 && aligned16(x) && aligned16(bias);
+#define GO(T, V) nhv_launch(add_row_bias_kernel<T, V>, gating_blocks(total / V), 256, 0, stream, (T*)x, (const T*)bias, width, total)
+  if (dtype == NHV_F32) { if (vec) GO(float, 8); else GO(float, 1); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
   else NHV_REQUIRE(false, "add_row_bias: unknown dtype %d", dtype);
+#undef GO
   NHV_CHECK_LAUNCH("add_row_bias");
   return 0;
 }
@@ -62,15 +96,24 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
   return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
 }
 
-template <typename T>
+template <typename T, int VEC>
 __global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total, float limit,
                                    float alpha) {
   pdl_prologue();
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < total; i += (size_t)gridDim.x * blockDim.x * VEC) {
     const size_t t = i / inter;
     const int c = (int)(i - t * inter);
     const T* row = gate_up + t * 2 * inter;
-    out[i] = from_f32<T>(clamped_glu(to_f32<T>(row[c]), to_f32<T>(row[inter + c]), limit, alpha));
+    if constexpr (VEC == 8) {
+      float gv[8], uv[8];
+      nhv_load8(gv, row + c);
+      nhv_load8(uv, row + inter + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) gv[e] = clamped_glu(gv[e], uv[e], limit, alpha);
+      nhv_store8(out + i, gv);
+    } else {
+      out[i] = from_f32<T>(clamped_glu(to_f32<T>(row[c]), to_f32<T>(row[inter + c]), limit, alpha));
+    }
   }
 }
 
@@ -79,13 +122,14 @@ NHV_API int nhv_clamped_glu(int dtype, void* out, const void* gate_up, int n_row
   if (n_rows == 0) return 0;
   NHV_REQUIRE(n_rows > 0 && inter > 0, "clamped_glu: bad sizes");
   const size_t total = (size_t)n_rows * inter;
-  const int blocks = (int)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
-  if (dtype == NHV_F32)
-    nhv_launch(clamped_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)gate_up, inter, total, limit, alpha);
-  else if (dtype == NHV_BF16)
-    nhv_launch(clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter,
-               total, limit, alpha);
+  const bool vec = inter % 8 == 0 && aligned16(out) && aligned16(gate_up);
+#define GO(T, V)                                                                                                   \
+  nhv_launch(clamped_glu_kernel<T, V>, gating_blocks(total / V), 256, 0, stream, (T*)out, (const T*)gate_up, inter, total, \
+             limit, alpha)
+  if (dtype == NHV_F32) { if (vec) GO(float, 8); else GO(float, 1); }
+  else if (dtype == NHV_BF16) { if (vec) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
   else NHV_REQUIRE(false, "clamped_glu: unknown dtype %d", dtype);
+#undef GO
   NHV_CHECK_LAUNCH("clamped_glu");
   return 0;
 }

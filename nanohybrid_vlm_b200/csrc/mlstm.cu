@@ -19,26 +19,11 @@
 #include <math.h>
 
 #include "nhv_common.cuh"
+#include "nhv_vec8.cuh"
 
 constexpr int ML_COLS = 16;
 
 __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
-
-// Eight consecutive elements as floats (p on a 16-byte boundary).
-__device__ __forceinline__ void ml_load8(float (&o)[8], const float* p) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-}
-__device__ __forceinline__ void ml_load8(float (&o)[8], const __nv_bfloat16* p) {
-  const uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __bfloat1622float2(h[i]);
-    o[2 * i] = f.x;
-    o[2 * i + 1] = f.y;
-  }
-}
 
 // Which row of its column a lane's r-th register holds (a column lives in PARTS lanes).  VEC (d in steps of 4 * PARTS):
 // groups of four consecutive rows, so that one 16-byte read of k and one of q from shared memory serve four rows, and
@@ -99,8 +84,8 @@ __global__ void __launch_bounds__(ML_COLS * ML_PARTS) mlstm_scan_kernel(
         const int tt = i / d8, c = (i - tt * d8) * 8;
         const T* row = proj + (size_t)(first + c0 + tt) * proj_stride;
         float q8[8], k8[8];
-        ml_load8(q8, row + q_off + c);
-        ml_load8(k8, row + k_off + c);
+        nhv_load8(q8, row + q_off + c);
+        nhv_load8(k8, row + k_off + c);
         float* qd = qs + tt * d + c;
         float* kd = ks + tt * d + c;
         *reinterpret_cast<float4*>(qd) = make_float4(q8[0] * qscale, q8[1] * qscale, q8[2] * qscale, q8[3] * qscale);

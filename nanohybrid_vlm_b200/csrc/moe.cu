@@ -18,6 +18,7 @@
 #include <math.h>
 
 #include "nhv_common.cuh"
+#include "nhv_vec8.cuh"
 
 // ---------------------------------------------------------------- router
 constexpr int MR_WARPS = 4;
@@ -281,33 +282,6 @@ NHV_API int nhv_moe_gemm_simt(int dtype, int first, void* out, const void* A, in
 }
 
 // ---------------------------------------------------------------- the weighted sum
-// Eight consecutive elements (16 bytes of bfloat16, 32 of float) as floats, and back.
-__device__ __forceinline__ void mc_load8(float (&o)[8], const float* p) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-}
-__device__ __forceinline__ void mc_load8(float (&o)[8], const __nv_bfloat16* p) {
-  const uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __bfloat1622float2(h[i]);
-    o[2 * i] = f.x;
-    o[2 * i + 1] = f.y;
-  }
-}
-__device__ __forceinline__ void mc_store8(float* p, const float (&v)[8]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void mc_store8(__nv_bfloat16* p, const float (&v)[8]) {
-  uint4 raw;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-  *reinterpret_cast<uint4*>(p) = raw;
-}
-
 // VEC: eight columns per thread and step (width in steps of 8, rows on 16-byte boundaries); the sums run in the same
 // order either way.
 template <typename T, bool VEC>
@@ -331,11 +305,11 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
   if constexpr (VEC) {
     for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, xv[8], v[8];
-      mc_load8(xv, x + (size_t)t * width + c);
+      nhv_load8(xv, x + (size_t)t * width + c);
       for (int k = 0; k < top; ++k) {
         const int p = pos[k];
         if (p >= 0) {
-          mc_load8(v, y + (size_t)p * width + c);
+          nhv_load8(v, y + (size_t)p * width + c);
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[k], v[i], acc[i]);
         } else if (p == -2) {
@@ -344,11 +318,11 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ y,
         }
       }
       if (shared) {
-        mc_load8(v, shared + (size_t)t * width + c);
+        nhv_load8(v, shared + (size_t)t * width + c);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = fmaf(sg, v[i], acc[i]);
       }
-      mc_store8(out + (size_t)t * width + c, acc);
+      nhv_store8(out + (size_t)t * width + c, acc);
     }
   } else {
     for (int c = threadIdx.x; c < width; c += blockDim.x) {

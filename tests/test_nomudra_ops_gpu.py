@@ -96,14 +96,19 @@ def test_dyntanh_forms(ops, dtype, width):
 
 # ---------------------------------------------------------------- small gated steps
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_gates_bias_and_clamped_unit(ops, dtype):
+@pytest.mark.parametrize("n,skip", [(70, 3), (72, 8), (1032, 16)], ids=["one_column_a_thread", "eight", "eight_wide"])
+def test_gates_bias_and_clamped_unit(ops, dtype, n, skip):
     g = torch.Generator().manual_seed(5)
-    T, n = 6, 70
-    wide = (2 * torch.randn(T, 2 * n + 3, generator=g)).to(dtype)
+    T = 6
+    wide = (2 * torch.randn(T, 2 * n + skip, generator=g)).to(dtype)
     x = torch.randn(T, n, generator=g).to(dtype)
     out = torch.empty(T, n, dtype=dtype, device="cuda")
-    ops.sigmoid_mul(out, dev(x), dev(wide)[:, 3:3 + n])
-    torch.testing.assert_close(out.cpu().to(F64), x.to(F64) * torch.sigmoid(wide[:, 3:3 + n].to(F64)), **tol(dtype))
+    ops.sigmoid_mul(out, dev(x), dev(wide)[:, skip:skip + n])
+    want = x.to(F64) * torch.sigmoid(wide[:, skip:skip + n].to(F64))
+    torch.testing.assert_close(out.cpu().to(F64), want, **tol(dtype))
+    inplace = dev(x.clone())
+    ops.sigmoid_mul(inplace, inplace, dev(wide)[:, skip:skip + n])               # the attention layer gates its heads in place
+    torch.testing.assert_close(inplace.cpu().to(F64), want, **tol(dtype))
     b = torch.randn(n, generator=g).to(dtype)
     y = dev(x.clone())
     ops.add_row_bias(y, dev(b))
